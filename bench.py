@@ -1,0 +1,379 @@
+#!/usr/bin/env python
+"""Benchmark of the ESP attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (N GPUs): ring causal prefill attention of ONE 262144-token sequence at the
+Llama-2-7B layer shape (32 q/kv heads x 128, bf16, Q/K/V ~ N(0,1), seeded), sharded over the N ranks
+in the reference's striped placement (token t on rank t mod N) with the KV blocks rotating around the
+NCCL ring.  A "step" is one full ring pass (state reset + N attention steps + N-1 exchanges).
+value = algorithmic TFLOP/s of the whole job: 4*D*H*T*(T+1)/2 FLOP per step / device time (max over ranks).
+
+The same JSON line carries: `roofline` (tensor-core bound, against the measured cuBLAS bf16 peak),
+`e2e` (same metric through the public Python API with HOST pinned inputs copied in and the output
+copied back inside the timed region), `cpu_baseline` (the CPU oracle on a bounded sample, rank 0,
+N=1 only), `decode` (distributed flash-decoding, HBM-bound, N=1 only: batch 64, lengths U[4096,65536],
+token-indexed pool with shuffled slots) and `clocks`.
+
+`--impl reference` times the CPU restatement of the reference path (oracle/) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, D = 32, 128
+T_TOTAL = 262144
+METRIC = "ring_prefill_attention_tflops"
+
+
+def prefill_flops(T: int) -> float:
+    return 4.0 * D * H * T * (T + 1) / 2.0
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=d["hbm_gbs"], tf_burst=d["bf16_tflops"], tf_sustained=d["bf16_tflops_sustained"], src="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, src="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of this process's GPU while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); pw.append(float(f[3]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm_sorted = sorted(sm)
+        return {"sm_mhz": sm_sorted[len(sm_sorted) // 2], "sm_max_mhz": max(mx), "power_w_max": max(pw),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference_arm(args):
+    """The reference path's CPU implementation (the oracle restatement) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from oracle import esp_oracle as O
+    cores = torch.get_num_threads()
+    Ts = int(os.environ.get("ESP_BENCH_CPU_TOKENS", "8192"))
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
+    ln = torch.tensor([Ts], dtype=torch.int32); z = torch.zeros(1, dtype=torch.int32)
+
+    def step():
+        o = torch.zeros(Ts, H, D, dtype=torch.bfloat16)
+        m = torch.full((Ts, H), float("-inf")); l = torch.zeros(Ts, H)
+        O.ring_step(q, k, v, o, m, l, z, ln, z, z, ln, z, 1)
+        return o
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    val = prefill_flops(Ts) / dt / 1e12
+    sample = f"one causal ring step over {Ts} tokens x {H} heads x {D} (bf16 inputs, fp32 math), FLOP-normalised"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"ring causal prefill attention, 1 seq x {T_TOTAL} tokens, {H}x{D}, striped over N GPUs",
+                   "note": "CPU arm runs a bounded sample of the same step"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def decode_bench(torch, peaks, steps=10, warmup=3):
+    """Distributed flash-decoding on one instance: stage 1 + merge over a shuffled token-indexed pool."""
+    from loongserve_b200 import flash_decoding as fd
+    dev = "cuda"
+    g = torch.Generator().manual_seed(0)
+    B = 64
+    lens = torch.randint(4096, 65537, (B,), generator=g)
+    total = int(lens.sum())
+    pool = torch.empty(total + 8, 2 * H, D, dtype=torch.bfloat16, device=dev)
+    gg = torch.Generator(device=dev).manual_seed(1)
+    chunk = 1 << 16
+    for s in range(0, pool.shape[0], chunk):
+        e = min(pool.shape[0], s + chunk)
+        pool[s:e] = torch.randn(e - s, 2 * H, D, generator=gg, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    q = torch.randn(B, H, D, generator=gg, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    mx = int(lens.max())
+    rt = torch.full((B, mx), 2147483647, dtype=torch.int32)
+    perm = torch.randperm(total, generator=g).to(torch.int32)
+    off = 0
+    for b in range(B):
+        n = int(lens[b]); rt[b, :n] = perm[off:off + n]; off += n
+    rt = rt.to(dev)
+    b_req = torch.arange(B, dtype=torch.int32, device=dev); b_len = lens.to(torch.int32).to(dev)
+    k, v = pool[:, :H], pool[:, H:]
+    bs = int(os.environ.get("ESP_BENCH_DECODE_BLOCK", "2048"))
+    nblk = (mx + bs - 1) // bs
+    mid_o = torch.empty(nblk, B, H, D, device=dev); mid_l = torch.empty(nblk, B, H, device=dev)
+    o = torch.empty(B, H, D, dtype=torch.bfloat16, device=dev); lse = torch.empty(B, H, device=dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    t1 = t2 = 0.0
+    for it in range(warmup + steps):
+        ev[0].record()
+        fd.flash_decoding_stage1(mid_o, mid_l, q, k, v, rt, b_req, b_len, mx, bs)
+        ev[1].record()
+        fd.flash_decoding_stage2(o, lse, b_len, mid_o, mid_l, bs)
+        ev[2].record()
+        torch.cuda.synchronize()
+        if it >= warmup:
+            t1 += ev[0].elapsed_time(ev[1]); t2 += ev[1].elapsed_time(ev[2])
+    t1 /= steps; t2 /= steps
+    nparts = int(((lens + bs - 1) // bs).sum())
+    # K+V rows read once, 4 B slot id per token, q, fp32 partial (o, lse) per (request, head, split)
+    alg_bytes = float(total) * (2 * H * D * 2) + float(total) * 4 + B * H * D * 2 + nparts * H * (D + 1) * 4
+    gbs = alg_bytes / (t1 * 1e-3) / 1e9
+    out = {"metric": "decode_attention_hbm_gbs", "value": gbs, "unit": "GB/s", "stage1_ms": t1, "merge_ms": t2,
+           "stage1_plus_merge_gbs": alg_bytes / ((t1 + t2) * 1e-3) / 1e9,
+           "config": {"workload": f"batch {B} x U[4096,65536] tokens ({total} total), {H}x{D} bf16, shuffled token-indexed pool, split {bs}",
+                      "l2": "pool (36 GB) far larger than L2"},
+           "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
+                        "traffic": None, "peak_source": peaks["src"]},
+           "algorithmic_bytes": alg_bytes, "gpu_launches_per_step": 2}
+    del pool
+    torch.cuda.empty_cache()
+    return out
+
+
+def cpu_baseline(torch):
+    from oracle import esp_oracle as O
+    Ts = int(os.environ.get("ESP_BENCH_CPU_TOKENS", "8192"))
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
+    ln = torch.tensor([Ts], dtype=torch.int32); z = torch.zeros(1, dtype=torch.int32)
+    best = None
+    for it in range(3):
+        o = torch.zeros(Ts, H, D, dtype=torch.bfloat16)
+        m = torch.full((Ts, H), float("-inf")); l = torch.zeros(Ts, H)
+        t0 = time.perf_counter()
+        O.ring_step(q, k, v, o, m, l, z, ln, z, z, ln, z, 1)
+        dt = time.perf_counter() - t0
+        if it > 0:
+            best = dt if best is None else min(best, dt)
+    return {"value": prefill_flops(Ts) / best / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"one causal ring step over {Ts} tokens x {H} heads x {D} (bf16 inputs, fp32 math, torch CPU), best of 2 after 1 warm-up, FLOP-normalised"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=T_TOTAL)
+    ap.add_argument("--layout", default="striped", choices=["striped", "contiguous"])
+    ap.add_argument("--no-overlap", action="store_true")
+    ap.add_argument("--skip-extras", action="store_true", help="skip e2e / decode / cpu baseline (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from loongserve_b200 import context_attention as ca
+    from loongserve_b200 import ring as ringmod
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    P = world
+    comm = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        from loongserve_b200 import rnccl
+        idt = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            idt = torch.tensor(rnccl.get_nccl_unique_id(), dtype=torch.uint8, device=dev)
+        dist.broadcast(idt, 0)
+        comm = rnccl.RNCCLComm(idt.cpu().tolist(), world, rank)
+
+    peaks = load_peaks()
+    T = args.tokens
+    striped = args.layout == "striped"
+    local_len, first, stride = ringmod.shard_lengths([T], P, striped)
+    metas = [ringmod.BlockMeta.from_lengths(local_len[r], first[r], dev) for r in range(P)]
+    Tl = local_len[rank][0]
+    max_tok = max(x[0] for x in local_len)
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q = torch.randn(Tl, H, D, generator=g, device=dev, dtype=torch.bfloat16)
+    kv_local = torch.randn(max_tok, 2 * H, D, generator=g, device=dev, dtype=torch.bfloat16)
+    recv = [torch.empty_like(kv_local) for _ in range(2 if P > 1 else 0)]
+    o = torch.empty_like(q)
+    m = torch.empty(Tl, H, device=dev); l = torch.empty(Tl, H, device=dev)
+
+    def init_fn(o_, m_, l_):
+        ca.init_attention_state(None, m_, l_)
+
+    def step():
+        if P == 1:
+            init_fn(o, m, l)
+            ca.context_attention_fwd(q, kv_local[:, :H], kv_local[:, H:], o, metas[0].start_loc, metas[0].seq_len,
+                                     metas[0].first_idx, metas[0].start_loc, metas[0].seq_len, metas[0].first_idx,
+                                     1, Tl, m, l)
+        else:
+            ringmod.ring_context_attention(q, kv_local, o, m, l, rank=rank, peers=list(range(P)), metas=metas,
+                                           stride=stride, max_len_in_batch=Tl, num_kv_heads=H, comm=comm,
+                                           recv_buffers=recv, attention_fn=ca.context_attention_fwd, init_fn=init_fn,
+                                           overlap=not args.no_overlap)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        tms = torch.tensor([ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+    st = ca.device_status()
+    flops = prefill_flops(T)
+    value = flops / (ms * 1e-3) / 1e12
+    per_gpu = value / P
+
+    # ---- end to end through the public API with host buffers (every step: H2D inputs, D2H output)
+    e2e = None
+    if not args.skip_extras:
+        hq = torch.empty(q.shape, dtype=q.dtype).pin_memory(); hq.copy_(q)
+        hkv = torch.empty(kv_local.shape, dtype=q.dtype).pin_memory(); hkv.copy_(kv_local)
+        ho = torch.empty(o.shape, dtype=o.dtype).pin_memory()
+
+        def e2e_step():
+            q.copy_(hq, non_blocking=True)
+            kv_local.copy_(hkv, non_blocking=True)
+            step()
+            ho.copy_(o, non_blocking=True)
+
+        e2e_step(); torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        n_e2e = 2
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
+        ems = e0.elapsed_time(e1) / n_e2e
+        if world > 1:
+            tms = torch.tensor([ems], device=dev)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            ems = float(tms.item())
+        e2e = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": (hq.numel() + hkv.numel()) * 2 * P, "d2h_bytes_per_step": ho.numel() * 2 * P,
+               "ms_per_step": ems, "steps": n_e2e}
+        del hq, hkv, ho
+
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": P, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": f"ring causal prefill attention, 1 seq x {T} tokens, {H} q/kv heads x {D}, bf16, "
+                                   f"{args.layout} over {P} GPU(s), {'overlapped' if not args.no_overlap else 'serialised'} NCCL ring",
+                       "l2": "inputs (q 2 GiB + kv 4 GiB per job) far larger than L2, no flush needed",
+                       "flop_per_step": flops},
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tf_sustained"], "unit": "TFLOP/s",
+                         "frac": per_gpu / peaks["tf_sustained"], "traffic": None, "peak_source": peaks["src"],
+                         "peak_kind": "sustained cuBLAS bf16 (kernel runs for seconds inside the timed loop)",
+                         "frac_of_burst_peak": per_gpu / peaks["tf_burst"], "per_gpu": True},
+            "clocks": clocks,
+            "gpu_launches": args.steps * (1 + P),
+            "device_status": list(st),
+        }
+        if e2e is not None:
+            out["e2e"] = e2e
+        if not args.skip_extras and P == 1:
+            del q, kv_local, o
+            torch.cuda.empty_cache()
+            out["decode"] = decode_bench(torch, peaks)
+            out["cpu_baseline"] = cpu_baseline(torch)
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        comm.close()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

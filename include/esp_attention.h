@@ -1,0 +1,196 @@
+/*
+ * esp_attention.h -- C ABI of the B200 (sm_100a) elastic-sequence-parallel attention library.
+ *
+ * Every entry point takes raw device pointers, explicit sizes/strides (in ELEMENTS unless a name says
+ * bytes) and a CUDA stream passed as void* (cudaStream_t).  No entry point allocates device memory
+ * or synchronises the device unless its comment says so.  Return value: ESP_OK (0) or a negative
+ * ESP_ERR_* code; esp_strerror() names it.  Kernels are launched asynchronously on `stream`.
+ *
+ * Each declaration cites the reference interface it replaces (path inside the reference project).
+ */
+#ifndef ESP_ATTENTION_H_
+#define ESP_ATTENTION_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ESP_OK 0
+#define ESP_ERR_BAD_ARG (-1)        /* null pointer, negative size, unsupported head_dim / dtype */
+#define ESP_ERR_ALIGNMENT (-2)      /* pointer or stride not aligned as the kernel needs (16 bytes) */
+#define ESP_ERR_CUDA (-3)           /* a CUDA runtime / driver call failed; see esp_last_cuda_error() */
+#define ESP_ERR_DEVICE_TIMEOUT (-4) /* a bounded in-kernel wait gave up (reported by esp_device_status) */
+#define ESP_ERR_UNSUPPORTED (-5)    /* valid request the library has no kernel for */
+#define ESP_ERR_NCCL (-6)           /* an NCCL call failed */
+#define ESP_ERR_TOO_LARGE (-7)      /* size beyond a fixed capacity stated by the entry point */
+
+#define ESP_DTYPE_F16 0
+#define ESP_DTYPE_BF16 1
+#define ESP_DTYPE_F32 2
+
+const char* esp_strerror(int code);
+/* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
+const char* esp_last_cuda_error(void);
+/* ABI version of this header (bumped on incompatible change). */
+int esp_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Ring prefill: one step of causal varlen attention with a running (o, m, l) state.
+ * Replaces context_attention_fwd / _fwd_kernel,
+ *   loongserve/models/llama/triton_kernel/ring_context_flashattention_nopad.py:191-284 (:13-188).
+ *
+ * q [q_tokens, Hq, D], k/v [kv_tokens, Hkv, D] (k and v may be the two halves of one
+ * [kv_tokens, 2*Hkv, D] buffer: pass the two base pointers and the shared strides), o like q,
+ * m/l fp32 [q_tokens, Hq] contiguous.  Last dimension contiguous everywhere; token and head strides
+ * in elements, multiples of 8.  Six int32 [batch] vectors as in the reference.  Key n of request b is
+ * visible to q row r iff  q_first[b] + r*s >= kv_first[b] + n*s  and  n < kv_len[b]
+ * (s = logical_sp_peers_num).
+ *
+ * State convention (same as the reference): m = running maximum of score*scale*log2(e), l = matching
+ * sum of 2^(.), o = NORMALISED output in `o_dtype` after every call.  Legal initial state:
+ * m = -inf, l = 0, o = anything.  Rows that see no key in this call are left unchanged.
+ * natural-log lse = ln2*m + ln(l).
+ *
+ * dtype: ESP_DTYPE_F16 or ESP_DTYPE_BF16 (q, k, v).  o_dtype: same as dtype, or ESP_DTYPE_F32 to
+ * carry the output in fp32 between ring steps.  head_dim must be 128.  sm_scale <= 0 selects
+ * head_dim^-0.5.  The host builds three TMA descriptors per call (no device work, no allocation).
+ */
+int esp_prefill_step(const void* q, int64_t q_stride_t, int64_t q_stride_h, int64_t q_tokens,
+                     const void* k, const void* v, int64_t kv_stride_t, int64_t kv_stride_h,
+                     int64_t kv_tokens,
+                     void* o, int64_t o_stride_t, int64_t o_stride_h, float* m, float* l,
+                     const int32_t* q_b_start_loc, const int32_t* q_b_seq_len,
+                     const int32_t* q_first_token_global_idx, const int32_t* kv_b_start_loc,
+                     const int32_t* kv_b_seq_len, const int32_t* kv_first_token_global_idx,
+                     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                     int32_t logical_sp_peers_num, int32_t max_q_b_seq_len, int32_t dtype,
+                     int32_t o_dtype, float sm_scale, void* stream);
+
+/* Reset the running state before the first ring step: o = 0, m = -inf, l = 0
+ * (longserve_transformer_layer_infer.py:123-126).  o may be NULL. */
+int esp_prefill_state_init(void* o, int64_t o_bytes, float* m, float* l, int64_t rows_times_heads,
+                           void* stream);
+
+/* lse[i] = ln2*m[i] + ln(l[i])  (-inf where l == 0). */
+int esp_prefill_lse(const float* m, const float* l, float* lse, int64_t n, void* stream);
+
+/* Device-side status of the bounded waits inside the prefill kernel on the current device:
+ * out[0] = 0 or ESP_ERR_DEVICE_TIMEOUT, out[1] = block index, out[2] = which wait, out[3] = detail.
+ * Synchronises the device.  `clear` != 0 resets it. */
+int esp_device_status(int32_t out[4], int32_t clear);
+
+/* ------------------------------------------------------------------------------------------------
+ * Distributed flash-decoding.
+ * esp_decode_stage1 replaces longserve_cuda_kernels.flash_decoding_stage1
+ *   (longserve_cuda_kernels/src/entrypoints.cpp:103-164, flash_decoding_stage1.cu:25-215).
+ * mid_o fp32 [num_blocks, batch, Hq, D], mid_lse fp32 [num_blocks, batch, Hq] (contiguous);
+ * q [batch, Hq, D] contiguous; k, v [pool, Hkv, D] views (strides in elements, last dim contiguous);
+ * req_to_tokens int32 [max_req, max_seq] (row stride max_seq); b_req_idx, b_seqlen int32 [batch].
+ * Block j of request b covers tokens [j*seq_block_size, min((j+1)*seq_block_size, len_b)); blocks
+ * past the length are not written.  Unlike the reference seq_block_size may be any positive value
+ * (the reference caps it at 256); head_dim must be 128.
+ */
+int esp_decode_stage1(float* mid_o, float* mid_lse, const void* q, const void* k, const void* v,
+                      int64_t k_stride_t, int64_t k_stride_h, int64_t v_stride_t, int64_t v_stride_h,
+                      const int32_t* req_to_tokens, int64_t req_to_tokens_stride,
+                      const int32_t* b_req_idx, const int32_t* b_seqlen, int32_t batch,
+                      int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                      int32_t max_len_in_batch, int32_t seq_block_size, int32_t dtype, float sm_scale,
+                      void* stream);
+
+/* esp_decode_merge replaces longserve_cuda_kernels.flash_decoding_stage2
+ *   (entrypoints.cpp:166-221, flash_decoding_stage2.cu:15-150): lse-merge of
+ * ceil(b_seqlen[b]/block_seq) partials per (request, head).  o_dtype F16/BF16/F32.
+ * A request with zero partials gets o = 0, lse = -inf (the reference leaves both unwritten). */
+int esp_decode_merge(void* o, float* out_lse, const int32_t* b_seqlen, const float* mid_o,
+                     const float* mid_lse, int32_t batch, int32_t num_heads, int32_t head_dim,
+                     int32_t num_blocks, int32_t block_seq, int32_t o_dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Token-indexed KV pool: scatter, registration, migration (all bit-exact copies / integer work).
+ * Rows are [heads2, D] with D contiguous; `row_stride` = token stride, `head_stride` = head stride.
+ * `elem_bytes` is 2 for fp16/bf16.  Index arrays may be int32 or int64 (`idx64` != 0).
+ */
+
+/* out[dest[i]] = src[i], i < n.  Replaces destindex_copy_kv
+ *   (loongserve/common/basemodel/triton_kernel/destindex_copy_kv.py:32-51). */
+int esp_kv_scatter(const void* src, int64_t src_row_stride, int64_t src_head_stride, void* out,
+                   int64_t out_row_stride, int64_t out_head_stride, const void* dest, int32_t idx64,
+                   int64_t n, int32_t heads2, int32_t head_dim, int32_t elem_bytes, void* stream);
+
+/* Keep-range of a passing striped block: begin = ceil((cache_begin - kv_first)/P), end likewise,
+ * new_len = end - begin.  Replaces pre_copy_and_register_kv
+ *   (loongserve/models/llama/triton_kernel/copy_and_register_kv.py:34-61). */
+int esp_kv_keep_range(const int32_t* cache_begin, const int32_t* cache_end, const int32_t* kv_first,
+                      int32_t num_peers, int32_t batch, int32_t* range_begin, int32_t* range_end,
+                      int32_t* new_len, void* stream);
+
+/* Copy the kept rows into pool slots mem_index[num_used + cumsum_prev[b] + n] and, when
+ * `should_register` != 0, write the slot ids to req_to_token[b_req_idx[b], cur_kv_cache_index[b] + n].
+ * Replaces destindex_copy_and_register_kv (copy_and_register_kv.py:123-169).
+ * new_len_cumsum is the int64 inclusive cumsum of new_len. */
+int esp_kv_scatter_register(int32_t batch, const int32_t* new_len, const int32_t* range_begin,
+                            const int32_t* range_end, const int64_t* new_len_cumsum, const void* kv,
+                            int64_t kv_row_stride, int64_t kv_head_stride,
+                            const int32_t* kv_b_start_loc, const int32_t* cur_kv_cache_index,
+                            const void* mem_index, int32_t idx64, void* pool, int64_t pool_row_stride,
+                            int64_t pool_head_stride, int32_t* req_to_token,
+                            int64_t req_to_token_stride, const int32_t* b_req_idx,
+                            int64_t num_used_mem_index, int32_t max_len_in_batch,
+                            int32_t should_register, int32_t heads2, int32_t head_dim,
+                            int32_t elem_bytes, void* stream);
+
+/* req_to_token[b_req_idx[i], b_seq_len[i]-1] = memindex[i].  Replaces copy_kv_index_to_req
+ *   (loongserve/common/basemodel/triton_kernel/copy_kv_index_to_req.py:22-38). */
+int esp_kv_index_register(int32_t* req_to_token, int64_t req_to_token_stride,
+                          const int32_t* b_req_idx, const int32_t* b_seq_len, const void* memindex,
+                          int32_t idx64, int32_t batch, void* stream);
+
+/* Prefill registration without the host loop: req_to_token[b_req_idx[b], 0:len_b] =
+ * alloc[start_b : start_b+len_b], start_b = exclusive cumsum of b_seq_len computed on the device.
+ * Replaces init_req_to_token_indexes (loongserve/common/infer_utils.py:1-13).  batch <= 65536. */
+int esp_kv_index_init(int32_t* req_to_token, int64_t req_to_token_stride, const int32_t* b_req_idx,
+                      const int32_t* b_seq_len, const void* alloc, int32_t idx64, int32_t batch,
+                      int32_t max_len_in_batch, void* stream);
+
+/* Decode-stage migration, sender side: gather the last num_tokens[b] tokens of each request, all
+ * layers, into send_buf [L, total, heads2, D] (contiguous) and zero mem_state of their slots.
+ * Replaces decoding_stage_migration_sender_kernel
+ *   (loongserve/models/llama/triton_kernel/decoding_stage_migration.py:71-95).
+ * num_tokens_cumsum = int32/int64-agnostic: pass the int64 inclusive cumsum. kv_cache is
+ * [L, slots, heads2, D] with `kv_layer_stride`, `kv_row_stride` in elements and contiguous rows. */
+int esp_mig_gather(void* send_buf, int64_t total_tokens, const int32_t* req_to_token,
+                   int64_t req_to_token_stride, int32_t* mem_state, const void* kv_cache,
+                   int64_t kv_layer_stride, int64_t kv_row_stride, const int32_t* request_ids,
+                   const int32_t* num_tokens, const int64_t* num_tokens_cumsum,
+                   const int32_t* b_seq_len, int32_t batch, int32_t max_num_tokens,
+                   int32_t num_layers, int32_t heads2, int32_t head_dim, int32_t elem_bytes,
+                   void* stream);
+
+/* Receiver side: scatter recv_buf into slots alloc_mem[cumsum_prev[b] + i] (all layers) and append
+ * the slot ids at req_to_token[request_ids[b], b_seq_len[b] + i].  Replaces
+ * decoding_stage_migration_receiver_kernel (decoding_stage_migration.py:160-184). */
+int esp_mig_scatter(const void* recv_buf, int64_t total_tokens, int32_t* req_to_token,
+                    int64_t req_to_token_stride, void* kv_cache, int64_t kv_layer_stride,
+                    int64_t kv_row_stride, const void* alloc_mem, int32_t idx64,
+                    const int32_t* request_ids, const int32_t* num_tokens,
+                    const int64_t* num_tokens_cumsum, const int32_t* b_seq_len, int32_t batch,
+                    int32_t max_num_tokens, int32_t num_layers, int32_t heads2, int32_t head_dim,
+                    int32_t elem_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Building-block self check (used by the test-suite): D[128,128] fp32 = A[128,128] * B^T through one
+ * tcgen05.mma chain, in the three operand forms the prefill kernel uses.
+ * mode 0: A and B K-major in shared memory (the Q*K^T form);
+ * mode 1: A K-major, B MN-major in shared memory (B given as [K=128, N=128] row-major, the P*V form);
+ * mode 2: A converted to 16-bit and staged in tensor memory, B MN-major (the P*V form actually used).
+ * a, b are device [128,128] of `dtype` row-major; d device fp32 [128,128]. */
+int esp_selftest_umma(const void* a, const void* b, float* d, int32_t mode, int32_t dtype,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ESP_ATTENTION_H_ */

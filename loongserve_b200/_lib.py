@@ -1,0 +1,108 @@
+"""ctypes bindings of the C ABI (include/esp_attention.h, include/esp_rnccl.h).
+
+There is no fallback: if the CUDA library is missing this module raises, and every op raises
+RuntimeError on a non-zero status.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ATTN_LIB = os.path.join(HERE, "libesp_attention.so")
+RNCCL_LIB = os.path.join(HERE, "libesp_rnccl.so")
+
+ESP_DTYPE_F16, ESP_DTYPE_BF16, ESP_DTYPE_F32 = 0, 1, 2
+
+_i32, _i64, _f32, _vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
+
+# name -> argtypes, exactly as declared in include/esp_attention.h
+ATTN_SIGNATURES = {
+    "esp_abi_version": [],
+    "esp_prefill_step": [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _vp,
+                         _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
+    "esp_prefill_state_init": [_vp, _i64, _vp, _vp, _i64, _vp],
+    "esp_prefill_lse": [_vp, _vp, _vp, _i64, _vp],
+    "esp_device_status": [C.POINTER(_i32), _i32],
+    "esp_decode_stage1": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _vp,
+                          _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
+    "esp_decode_merge": [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp],
+    "esp_kv_scatter": [_vp, _i64, _i64, _vp, _i64, _i64, _vp, _i32, _i64, _i32, _i32, _i32, _vp],
+    "esp_kv_keep_range": [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp],
+    "esp_kv_scatter_register": [_i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i32, _vp, _i64,
+                                _i64, _vp, _i64, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp],
+    "esp_kv_index_register": [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _vp],
+    "esp_kv_index_init": [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _vp],
+    "esp_mig_gather": [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
+                       _i32, _i32, _i32, _vp],
+    "esp_mig_scatter": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32,
+                        _i32, _i32, _i32, _i32, _vp],
+    "esp_selftest_umma": [_vp, _vp, _vp, _i32, _i32, _vp],
+}
+ATTN_STRING_FUNCS = {"esp_strerror": [_i32], "esp_last_cuda_error": []}
+
+RNCCL_SIGNATURES = {
+    "esp_rnccl_unique_id": [C.POINTER(C.c_uint8)],
+    "esp_rnccl_create": [C.POINTER(C.c_uint8), _i32, _i32, C.POINTER(_vp)],
+    "esp_rnccl_destroy": [_vp],
+    "esp_rnccl_group_start": [_vp],
+    "esp_rnccl_group_end": [_vp],
+    "esp_rnccl_send": [_vp, _vp, _i64, _i32],
+    "esp_rnccl_recv": [_vp, _vp, _i64, _i32],
+    "esp_rnccl_fence_in": [_vp, _vp],
+    "esp_rnccl_fence_out": [_vp, _vp],
+}
+
+_attn = None
+_rnccl = None
+
+
+def attn():
+    """The attention library, loaded once.  Raises if it has not been built."""
+    global _attn
+    if _attn is None:
+        if not os.path.exists(ATTN_LIB):
+            raise RuntimeError(f"{ATTN_LIB} is missing: run `python -m loongserve_b200.build` (no CPU fallback exists)")
+        lib = C.CDLL(ATTN_LIB, mode=C.RTLD_GLOBAL)
+        for name, args in ATTN_SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = _i32
+        for name, args in ATTN_STRING_FUNCS.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = C.c_char_p
+        _attn = lib
+    return _attn
+
+
+def rnccl():
+    """The raw NCCL layer, loaded once (import torch first so that one NCCL copy serves the process)."""
+    global _rnccl
+    if _rnccl is None:
+        if not os.path.exists(RNCCL_LIB):
+            raise RuntimeError(f"{RNCCL_LIB} is missing: run `python -m loongserve_b200.build`")
+        lib = C.CDLL(RNCCL_LIB, mode=C.RTLD_GLOBAL)
+        for name, args in RNCCL_SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = _i32
+        lib.esp_rnccl_stream.argtypes = [_vp]
+        lib.esp_rnccl_stream.restype = _vp
+        lib.esp_rnccl_last_error.argtypes = []
+        lib.esp_rnccl_last_error.restype = C.c_char_p
+        _rnccl = lib
+    return _rnccl
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        lib = attn()
+        msg = lib.esp_strerror(rc).decode()
+        detail = lib.esp_last_cuda_error().decode()
+        raise RuntimeError(f"{what} failed: {msg} ({rc})" + (f": {detail}" if detail and rc == -3 else ""))
+
+
+def check_rnccl(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed ({rc}): {rnccl().esp_rnccl_last_error().decode()}")

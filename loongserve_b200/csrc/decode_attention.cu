@@ -1,0 +1,327 @@
+// Distributed flash-decoding for a token-indexed (page size 1) KV pool.
+//
+// Stage 1 (split-KV partial attention) is HBM-bound: every local K and V head row (D x 2 B = 256 B)
+// is read exactly once per kv head with 16-byte non-allocating loads; a half-warp covers one row, so
+// a warp instruction fetches two whole rows, and each lane keeps 2 x UNROLL such loads in flight.
+// All q heads that share a kv head are served by the same loaded rows.  One pass (online softmax in
+// base 2), warp-shuffle reductions, no atomics.  Algorithmic bytes per local token per kv head:
+// 512 B of K+V + 4 B slot id per CTA that visits it; plus q and the fp32 partial (o, lse) per block.
+//
+// Stage 2 merges the partials of one (request, head) with one warp: weights exp(lse_j - max) are
+// computed lane-parallel, then the [D] rows are accumulated with float4 loads.
+#include "esp_common.cuh"
+
+namespace esp {
+
+constexpr int kDecThreads = 128;          // 4 warps, 8 half-warps
+constexpr int kDecUnroll = 4;             // tokens per half-warp per step
+constexpr int kDecChunk = 1024;           // slot ids staged in shared memory per chunk
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+template <typename T, int G>
+__global__ void __launch_bounds__(kDecThreads) decode_stage1_kernel(
+    float* __restrict__ mid_o, float* __restrict__ mid_lse, const T* __restrict__ q,
+    const T* __restrict__ k, const T* __restrict__ v, int64_t k_stride_t, int64_t k_stride_h,
+    int64_t v_stride_t, int64_t v_stride_h, const int32_t* __restrict__ req_to_tokens,
+    int64_t rtt_stride, const int32_t* __restrict__ b_req_idx, const int32_t* __restrict__ b_seqlen,
+    int batch, int num_q_heads, int group /* q heads per kv head */, int seq_block_size,
+    float scale_log2) {
+    const int blk = blockIdx.x;
+    const int hg = blockIdx.y;            // group of G consecutive q heads
+    const int b = blockIdx.z;
+    const int len = b_seqlen[b];
+    const int t0 = blk * seq_block_size;
+    const int t1 = min(t0 + seq_block_size, len);
+    if (t1 <= t0) return;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int half = lane >> 4, hl = lane & 15;
+    const int slot_in_cta = warp * 2 + half;          // 0..7: which token of each group of 8
+    const int h0 = hg * G;
+    const int kvh = h0 / group;
+
+    __shared__ int32_t s_slots[kDecChunk];
+    __shared__ float s_red[4][G][128 + 2];
+
+    // q (pre-scaled into the log2 domain), 8 dims per lane
+    float qf[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const uint4 qv = *reinterpret_cast<const uint4*>(q + ((int64_t)b * num_q_heads + h0 + g) * 128 + hl * 8);
+        const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = Cvt<T>::to_f2(w[i]);
+            qf[g][2 * i] = f.x * scale_log2;
+            qf[g][2 * i + 1] = f.y * scale_log2;
+        }
+    }
+
+    float m_run[G], l_run[G], acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m_run[g] = -INFINITY; l_run[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+    }
+
+    const int32_t* rtt = req_to_tokens + (int64_t)b_req_idx[b] * rtt_stride;
+    const T* kbase = k + (int64_t)kvh * k_stride_h + hl * 8;
+    const T* vbase = v + (int64_t)kvh * v_stride_h + hl * 8;
+
+    for (int c0 = t0; c0 < t1; c0 += kDecChunk) {
+        const int cn = min(kDecChunk, t1 - c0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < cn; i += kDecThreads) s_slots[i] = rtt[c0 + i];
+        __syncthreads();
+        // each step covers 8 * kDecUnroll tokens of the chunk
+        for (int base = 0; base < cn; base += 8 * kDecUnroll) {
+            uint4 kr[kDecUnroll], vr[kDecUnroll];
+            bool valid[kDecUnroll];
+#pragma unroll
+            for (int u = 0; u < kDecUnroll; ++u) {
+                const int ti = base + u * 8 + slot_in_cta;
+                valid[u] = ti < cn;
+                const int64_t slot = s_slots[valid[u] ? ti : cn - 1];
+                kr[u] = ld_nc_v4(kbase + slot * k_stride_t);
+                vr[u] = ld_nc_v4(vbase + slot * v_stride_t);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float s[kDecUnroll];
+#pragma unroll
+                for (int u = 0; u < kDecUnroll; ++u) {
+                    const uint32_t w[4] = {kr[u].x, kr[u].y, kr[u].z, kr[u].w};
+                    float d = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = Cvt<T>::to_f2(w[i]);
+                        d = fmaf(qf[g][2 * i], f.x, d);
+                        d = fmaf(qf[g][2 * i + 1], f.y, d);
+                    }
+                    s[u] = d;
+                }
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) {
+#pragma unroll
+                    for (int u = 0; u < kDecUnroll; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
+                }
+                float m_new = m_run[g];
+#pragma unroll
+                for (int u = 0; u < kDecUnroll; ++u) {
+                    s[u] = valid[u] ? s[u] : -INFINITY;
+                    m_new = fmaxf(m_new, s[u]);
+                }
+                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                const float alpha = exp2f(m_run[g] - m_use);
+                float p[kDecUnroll], psum = 0.f;
+#pragma unroll
+                for (int u = 0; u < kDecUnroll; ++u) { p[u] = exp2f(s[u] - m_use); psum += p[u]; }
+                l_run[g] = l_run[g] * alpha + psum;
+                m_run[g] = m_new;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[g][i] *= alpha;
+#pragma unroll
+                for (int u = 0; u < kDecUnroll; ++u) {
+                    const uint32_t w[4] = {vr[u].x, vr[u].y, vr[u].z, vr[u].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = Cvt<T>::to_f2(w[i]);
+                        acc[g][2 * i] = fmaf(p[u], f.x, acc[g][2 * i]);
+                        acc[g][2 * i + 1] = fmaf(p[u], f.y, acc[g][2 * i + 1]);
+                    }
+                }
+            }
+        }
+    }
+
+    // combine the two half-warps, then the four warps
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const float m_o = __shfl_xor_sync(0xffffffffu, m_run[g], 16);
+        const float l_o = __shfl_xor_sync(0xffffffffu, l_run[g], 16);
+        const float m_new = fmaxf(m_run[g], m_o);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float a_self = exp2f(m_run[g] - m_use), a_oth = exp2f(m_o - m_use);
+        l_run[g] = l_run[g] * a_self + l_o * a_oth;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, acc[g][i], 16);
+            acc[g][i] = acc[g][i] * a_self + other * a_oth;
+        }
+        m_run[g] = m_new;
+        if (half == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s_red[warp][g][hl * 8 + i] = acc[g][i];
+            if (hl == 0) { s_red[warp][g][128] = m_run[g]; s_red[warp][g][129] = l_run[g]; }
+        }
+    }
+    __syncthreads();
+    const int d = threadIdx.x;   // 128 threads == 128 dims
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, s_red[w][g][128]);
+        float L = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float a = exp2f(s_red[w][g][128] - M);   // M is finite: the block has >= 1 token
+            L += s_red[w][g][129] * a;
+            o += s_red[w][g][d] * a;
+        }
+        const int64_t row = ((int64_t)blk * batch + b) * num_q_heads + h0 + g;
+        mid_o[row * 128 + d] = o / L;
+        if (d == 0) mid_lse[row] = (M + log2f(L)) * kLn2;
+    }
+}
+
+template <typename OT> __device__ __forceinline__ void store4(OT* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<__half>(__half* p, float4 v) {
+    uint2 u = make_uint2(Cvt<__half>::pack(v.x, v.y), Cvt<__half>::pack(v.z, v.w));
+    *reinterpret_cast<uint2*>(p) = u;
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+    uint2 u = make_uint2(Cvt<__nv_bfloat16>::pack(v.x, v.y), Cvt<__nv_bfloat16>::pack(v.z, v.w));
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+// One warp per (request, head); D = 128 -> 4 dims per lane.  4 warps per CTA.
+template <typename OT>
+__global__ void __launch_bounds__(128) decode_merge_kernel(
+    OT* __restrict__ o, float* __restrict__ out_lse, const int32_t* __restrict__ b_seqlen,
+    const float* __restrict__ mid_o, const float* __restrict__ mid_lse, int batch, int num_heads,
+    int num_blocks, int block_seq) {
+    const int lane = threadIdx.x & 31;
+    const int64_t pair = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (pair >= (int64_t)batch * num_heads) return;
+    const int b = (int)(pair / num_heads);
+    const int len = b_seqlen[b];
+    int n = len <= 0 ? 0 : (len + block_seq - 1) / block_seq;
+    if (n > num_blocks) n = num_blocks;
+    const int64_t bh = (int64_t)batch * num_heads;
+    float M = -INFINITY;
+    for (int j = lane; j < n; j += 32) M = fmaxf(M, mid_lse[j * bh + pair]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float wsum = 0.f;
+    if (M > -INFINITY) {
+        for (int j0 = 0; j0 < n; j0 += 32) {
+            const int j = j0 + lane;
+            const float wl = j < n ? __expf(mid_lse[j * bh + pair] - M) : 0.f;
+            wsum += wl;
+            const int cnt = min(32, n - j0);
+#pragma unroll 4
+            for (int jj = 0; jj < cnt; ++jj) {
+                const float w = __shfl_sync(0xffffffffu, wl, jj);
+                if (w > 0.f) {
+                    const float4 x = *reinterpret_cast<const float4*>(mid_o + ((j0 + jj) * bh + pair) * 128 + lane * 4);
+                    acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y);
+                    acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
+                }
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, off);
+        const float inv = 1.f / wsum;
+        acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+    }
+    store4<OT>(o + pair * 128 + lane * 4, acc);
+    if (lane == 0) out_lse[pair] = (M > -INFINITY) ? M + __logf(wsum) : -INFINITY;
+}
+
+template <typename T>
+static int launch_stage1(float* mid_o, float* mid_lse, const void* q, const void* k, const void* v,
+                         int64_t kst, int64_t ksh, int64_t vst, int64_t vsh, const int32_t* rtt,
+                         int64_t rtt_stride, const int32_t* b_req_idx, const int32_t* b_seqlen,
+                         int batch, int Hq, int Hkv, int max_len, int bs, float scale_log2,
+                         cudaStream_t s) {
+    const int group = Hq / Hkv;
+    const int nblk = (max_len + bs - 1) / bs;
+    int G = 1;
+    if (group % 8 == 0) G = 8; else if (group % 4 == 0) G = 4; else if (group % 2 == 0) G = 2;
+    dim3 grid(nblk, Hq / G, batch);
+#define ESP_S1(GG) decode_stage1_kernel<T, GG><<<grid, kDecThreads, 0, s>>>(mid_o, mid_lse, (const T*)q, \
+        (const T*)k, (const T*)v, kst, ksh, vst, vsh, rtt, rtt_stride, b_req_idx, b_seqlen, batch, Hq, \
+        group, bs, scale_log2)
+    switch (G) {
+        case 8: ESP_S1(8); break;
+        case 4: ESP_S1(4); break;
+        case 2: ESP_S1(2); break;
+        default: ESP_S1(1); break;
+    }
+#undef ESP_S1
+    ESP_LAUNCH_CHECK("decode_stage1_kernel");
+    return ESP_OK;
+}
+
+}  // namespace esp
+
+using namespace esp;
+
+extern "C" int esp_decode_stage1(float* mid_o, float* mid_lse, const void* q, const void* k,
+                                 const void* v, int64_t k_stride_t, int64_t k_stride_h,
+                                 int64_t v_stride_t, int64_t v_stride_h, const int32_t* req_to_tokens,
+                                 int64_t req_to_tokens_stride, const int32_t* b_req_idx,
+                                 const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
+                                 int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
+                                 int32_t seq_block_size, int32_t dtype, float sm_scale, void* stream) {
+    if (batch == 0 || max_len_in_batch <= 0) return ESP_OK;
+    if (!mid_o || !mid_lse || !q || !k || !v || !req_to_tokens || !b_req_idx || !b_seqlen || batch < 0 ||
+        num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads || seq_block_size <= 0)
+        return ESP_ERR_BAD_ARG;
+    if (head_dim != 128) return ESP_ERR_UNSUPPORTED;
+    if (batch > 65535 || num_q_heads > 65535) return ESP_ERR_TOO_LARGE;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || (k_stride_t % 8) || (k_stride_h % 8) ||
+        (v_stride_t % 8) || (v_stride_h % 8))
+        return ESP_ERR_ALIGNMENT;
+    const float scale = (sm_scale > 0.f ? sm_scale : 1.0f / sqrtf((float)head_dim)) * kLog2e;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == ESP_DTYPE_F16)
+        return launch_stage1<__half>(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t,
+                                     v_stride_h, req_to_tokens, req_to_tokens_stride, b_req_idx,
+                                     b_seqlen, batch, num_q_heads, num_kv_heads, max_len_in_batch,
+                                     seq_block_size, scale, s);
+    if (dtype == ESP_DTYPE_BF16)
+        return launch_stage1<__nv_bfloat16>(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t,
+                                            v_stride_h, req_to_tokens, req_to_tokens_stride, b_req_idx,
+                                            b_seqlen, batch, num_q_heads, num_kv_heads,
+                                            max_len_in_batch, seq_block_size, scale, s);
+    return ESP_ERR_BAD_ARG;
+}
+
+extern "C" int esp_decode_merge(void* o, float* out_lse, const int32_t* b_seqlen, const float* mid_o,
+                                const float* mid_lse, int32_t batch, int32_t num_heads,
+                                int32_t head_dim, int32_t num_blocks, int32_t block_seq,
+                                int32_t o_dtype, void* stream) {
+    if (batch == 0) return ESP_OK;
+    if (!o || !out_lse || !b_seqlen || !mid_o || !mid_lse || batch < 0 || num_heads <= 0 ||
+        num_blocks < 0 || block_seq <= 0)
+        return ESP_ERR_BAD_ARG;
+    if (head_dim != 128) return ESP_ERR_UNSUPPORTED;
+    if (!aligned16(mid_o) || !aligned16(o)) return ESP_ERR_ALIGNMENT;
+    const int64_t pairs = (int64_t)batch * num_heads;
+    const unsigned grid = (unsigned)((pairs + 3) / 4);
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (o_dtype) {
+        case ESP_DTYPE_F32:
+            decode_merge_kernel<float><<<grid, 128, 0, s>>>((float*)o, out_lse, b_seqlen, mid_o, mid_lse,
+                                                           batch, num_heads, num_blocks, block_seq);
+            break;
+        case ESP_DTYPE_F16:
+            decode_merge_kernel<__half><<<grid, 128, 0, s>>>((__half*)o, out_lse, b_seqlen, mid_o,
+                                                            mid_lse, batch, num_heads, num_blocks, block_seq);
+            break;
+        case ESP_DTYPE_BF16:
+            decode_merge_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>((__nv_bfloat16*)o, out_lse, b_seqlen,
+                                                                   mid_o, mid_lse, batch, num_heads,
+                                                                   num_blocks, block_seq);
+            break;
+        default: return ESP_ERR_BAD_ARG;
+    }
+    ESP_LAUNCH_CHECK("decode_merge_kernel");
+    return ESP_OK;
+}

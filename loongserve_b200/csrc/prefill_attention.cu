@@ -1,0 +1,565 @@
+// Ring-prefill attention step for sm_100a: causal varlen flash attention of the local q rows against
+// one (local or remote) KV block, merged into the running (o, m, l) state.
+//
+// One CTA owns 256 consecutive q rows of one (request, head) as two 128-row tiles.  Warp roles:
+//   warps 0-3  softmax of tile 0 (one thread per row), warps 4-7 softmax of tile 1,
+//   warp 8     TMA producer (Q tiles once, then K_0 V_0 K_1 V_1 ... through a ring of 32 KiB stages),
+//   warp 9     tcgen05.mma issuer and owner of the tensor-memory allocation.
+// Per kv tile and q tile:  S = Q K^T (tcgen05.mma, both operands K-major in 128B-swizzled smem, fp32
+// accumulator in tensor memory) -> softmax threads read their row with tcgen05.ld, apply the mask only
+// on diagonal/tail tiles, keep a running base-2 maximum with lazy rescaling of O, write P as packed
+// 16-bit back into the S columns -> O += P V (tcgen05.mma, A from tensor memory, V MN-major in smem).
+// The two q tiles ping-pong: while the tensor core runs tile 0's PV and next S, tile 1's softmax runs.
+// Tensor-memory map (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P aliases S.
+//
+// Roofline: tensor-core bound; algorithmic FLOPs = 4 * D * (visible q,k pairs) per head.
+// Every mbarrier wait is bounded; on expiry the kernel records a status word and drains.
+#include <cuda.h>
+
+#include "esp_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace esp {
+
+using namespace ptx;
+
+constexpr int BM = 128;               // rows per q tile
+constexpr int QT = 2;                 // q tiles per CTA
+constexpr int BN = 128;               // keys per kv tile
+constexpr int HD = 128;               // head dim
+constexpr int NSTAGE = 4;             // K/V ring stages
+constexpr int TILE_BYTES = BN * HD * 2;
+constexpr int HALF_BYTES = TILE_BYTES / 2;   // 64 head-dim columns x 128 rows (one swizzle-128B panel)
+constexpr int NUM_THREADS = 320;
+constexpr int TMEM_COLS = 512;
+constexpr long long kWaitLimitCycles = 2000000000LL;   // about a second
+constexpr float kRescaleThreshold = 8.0f;              // lazy O rescale: tolerate 2^8 growth
+
+enum BarIdx { B_QFULL = 0, B_KVFULL = 2, B_KVEMPTY = 2 + NSTAGE, B_SFULL = 2 + 2 * NSTAGE,
+              B_PREADY = 4 + 2 * NSTAGE, B_ODONE = 6 + 2 * NSTAGE, B_COUNT = 8 + 2 * NSTAGE };
+
+constexpr int SMEM_Q = 0;
+constexpr int SMEM_KV = QT * TILE_BYTES;
+constexpr int SMEM_BAR = SMEM_KV + NSTAGE * TILE_BYTES;
+constexpr int SMEM_MISC = SMEM_BAR + B_COUNT * 8;
+constexpr int SMEM_TOTAL = SMEM_MISC + 16;
+constexpr int SMEM_DYN = SMEM_TOTAL + 1024;            // slack to align the base to 1024 B
+
+__device__ int g_esp_status[4];
+
+struct PrefillParams {
+    void* o; float* m; float* l;
+    int64_t o_stride_t, o_stride_h;
+    const int32_t* q_start; const int32_t* q_len; const int32_t* q_first;
+    const int32_t* kv_start; const int32_t* kv_len; const int32_t* kv_first;
+    int num_q_heads, group, stride_s, num_qblocks;
+    float scale_log2;
+};
+
+__device__ __noinline__ void report_timeout(int which, int detail) {
+    if (atomicCAS(&g_esp_status[0], 0, ESP_ERR_DEVICE_TIMEOUT) == 0) {
+        g_esp_status[1] = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        g_esp_status[2] = which;
+        g_esp_status[3] = detail;
+    }
+}
+
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* s_abort, int which, int detail) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0) {
+            if (*s_abort) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                report_timeout(which, detail);
+                *s_abort = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+template <typename T> struct Fmt;
+template <> struct Fmt<__half> { static constexpr uint32_t kAB = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t kAB = 1; };
+
+template <typename OT> __device__ __forceinline__ void load_row32(const OT* p, float (&x)[32]);
+template <> __device__ __forceinline__ void load_row32<float>(const float* p, float (&x)[32]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float4 v = *reinterpret_cast<const float4*>(p + 4 * i);
+        x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+    }
+}
+template <typename OT> __device__ __forceinline__ void load_row32_16(const OT* p, float (&x)[32]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p + 8 * i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = Cvt<OT>::to_f2(w[k]);
+            x[8 * i + 2 * k] = f.x; x[8 * i + 2 * k + 1] = f.y;
+        }
+    }
+}
+template <> __device__ __forceinline__ void load_row32<__half>(const __half* p, float (&x)[32]) { load_row32_16<__half>(p, x); }
+template <> __device__ __forceinline__ void load_row32<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[32]) { load_row32_16<__nv_bfloat16>(p, x); }
+
+template <typename OT> __device__ __forceinline__ void store_row32(OT* p, const float (&x)[32]);
+template <> __device__ __forceinline__ void store_row32<float>(float* p, const float (&x)[32]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        *reinterpret_cast<float4*>(p + 4 * i) = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+}
+template <typename OT> __device__ __forceinline__ void store_row32_16(OT* p, const float (&x)[32]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 v;
+        v.x = Cvt<OT>::pack(x[8 * i], x[8 * i + 1]); v.y = Cvt<OT>::pack(x[8 * i + 2], x[8 * i + 3]);
+        v.z = Cvt<OT>::pack(x[8 * i + 4], x[8 * i + 5]); v.w = Cvt<OT>::pack(x[8 * i + 6], x[8 * i + 7]);
+        *reinterpret_cast<uint4*>(p + 8 * i) = v;
+    }
+}
+template <> __device__ __forceinline__ void store_row32<__half>(__half* p, const float (&x)[32]) { store_row32_16<__half>(p, x); }
+template <> __device__ __forceinline__ void store_row32<__nv_bfloat16>(__nv_bfloat16* p, const float (&x)[32]) { store_row32_16<__nv_bfloat16>(p, x); }
+
+// ------------------------------------------------------------------------------------------------
+template <typename T, typename OT>
+__global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
+    const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+    const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar0 = smem_base + SMEM_BAR;
+    auto bar = [bar0](int i) { return bar0 + 8u * i; };
+    volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem_gen + SMEM_MISC);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem_gen + SMEM_MISC + 4);
+    volatile int* s_skip = reinterpret_cast<volatile int*>(smem_gen + SMEM_MISC + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = p.num_qblocks - 1 - (int)blockIdx.x;      // heaviest q block first
+    const int head = blockIdx.y, b = blockIdx.z;
+    const int kvh = head / p.group;
+
+    const int q_len = p.q_len[b];
+    const int m0 = qb * (QT * BM);
+    if (m0 >= q_len) return;
+    const int kv_len = p.kv_len[b];
+    const int q_start = p.q_start[b], kv_start = p.kv_start[b];
+    // key n visible to local row r  <=>  n <= r - delta  and  n < kv_len
+    const int dnum = p.kv_first[b] - p.q_first[b];
+    const int delta = dnum >= 0 ? (dnum + p.stride_s - 1) / p.stride_s : -((-dnum) / p.stride_s);
+    int n_tiles[QT];
+#pragma unroll
+    for (int t = 0; t < QT; ++t) {
+        const int r0 = m0 + t * BM;
+        int cnt = 0;
+        if (r0 < q_len) {
+            const int last_row = min(r0 + BM - 1, q_len - 1);
+            const int range = max(0, min(last_row - delta + 1, kv_len));
+            cnt = (range + BN - 1) / BN;
+        }
+        n_tiles[t] = cnt;
+    }
+    const int nmax = max(n_tiles[0], n_tiles[1]);
+    if (nmax == 0) return;      // nothing visible: state unchanged
+
+    if (threadIdx.x == 0) {
+        *s_abort = 0;
+        *s_skip = (*reinterpret_cast<volatile int*>(&g_esp_status[0]) != 0);
+        for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i >= B_PREADY && i < B_PREADY + QT) ? BM : 1);
+        fence_barrier_init();
+    }
+    if (warp == 8 && lane == 0) {
+        prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
+    }
+    __syncthreads();
+    if (*s_skip) return;        // an earlier CTA reported a timeout: drain the grid quickly
+    if (warp == 9) {
+        tmem_alloc(smem_base + SMEM_MISC, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+#pragma unroll
+            for (int t = 0; t < QT; ++t) {
+                if (n_tiles[t] > 0) {
+                    const uint32_t dst = smem_base + SMEM_Q + t * TILE_BYTES;
+                    mbar_expect_tx(bar(B_QFULL + t), TILE_BYTES);
+                    tma_load_3d(dst, &tm_q, bar(B_QFULL + t), 0, head, q_start + m0 + t * BM);
+                    tma_load_3d(dst + HALF_BYTES, &tm_q, bar(B_QFULL + t), 64, head, q_start + m0 + t * BM);
+                }
+            }
+            for (int r = 0; r < 2 * nmax; ++r) {
+                const int stage = r % NSTAGE, use = r / NSTAGE;
+                if (use > 0 && !bounded_wait(bar(B_KVEMPTY + stage), (use - 1) & 1, s_abort, 1, r)) break;
+                const int j = r >> 1;
+                const CUtensorMap* tm = (r & 1) ? &tm_v : &tm_k;
+                const uint32_t dst = smem_base + SMEM_KV + stage * TILE_BYTES;
+                mbar_expect_tx(bar(B_KVFULL + stage), TILE_BYTES);
+                tma_load_3d(dst, tm, bar(B_KVFULL + stage), 0, kvh, kv_start + j * BN);
+                tma_load_3d(dst + HALF_BYTES, tm, bar(B_KVFULL + stage), 64, kvh, kv_start + j * BN);
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc_s = make_idesc(Fmt<T>::kAB, 0, BM, BN);
+        constexpr uint32_t idesc_pv = make_idesc(Fmt<T>::kAB, 1, BM, HD);
+        auto issue_s = [&](int t, int stage) {
+            const uint32_t qa = smem_base + SMEM_Q + t * TILE_BYTES;
+            const uint32_t kb = smem_base + SMEM_KV + stage * TILE_BYTES;
+#pragma unroll
+            for (int k = 0; k < HD / 16; ++k) {
+                const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+                umma_ss(tmem_base + t * BN, desc_kmajor_sw128(qa + off), desc_kmajor_sw128(kb + off), idesc_s, k > 0);
+            }
+        };
+        auto issue_pv = [&](int t, int stage, bool acc) {
+            const uint32_t vb = smem_base + SMEM_KV + stage * TILE_BYTES;
+#pragma unroll
+            for (int k = 0; k < BN / 16; ++k) {
+                umma_ts(tmem_base + QT * BN + t * HD, tmem_base + t * BN + k * 8,
+                        desc_mnmajor_sw128(vb + k * 2048, HALF_BYTES), idesc_pv, (acc || k > 0) ? 1u : 0u);
+            }
+        };
+        bool ok = true;
+#pragma unroll
+        for (int t = 0; t < QT; ++t)
+            if (n_tiles[t] > 0) ok = ok && bounded_wait(bar(B_QFULL + t), 0, s_abort, 2, t);
+        ok = ok && bounded_wait(bar(B_KVFULL + 0), 0, s_abort, 3, 0);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after();
+            if (lane == 0) {
+#pragma unroll
+                for (int t = 0; t < QT; ++t)
+                    if (n_tiles[t] > 0) { issue_s(t, 0); umma_commit(bar(B_SFULL + t)); }
+                umma_commit(bar(B_KVEMPTY + 0));
+            }
+            for (int j = 0; j < nmax && ok; ++j) {
+                const int rv = 2 * j + 1, sv = rv % NSTAGE;
+                ok = bounded_wait(bar(B_KVFULL + sv), (rv / NSTAGE) & 1, s_abort, 4, j);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if ((j + 1) * BN > kv_len) {
+                    // tail tile: rows past the request's last key may hold anything (even NaN); P is 0
+                    // there, so make V finite by zeroing those rows in shared memory.
+                    const int first_bad = kv_len - j * BN;
+                    uint8_t* vs = smem_gen + SMEM_KV + sv * TILE_BYTES;
+                    for (int i = first_bad * 8 + lane; i < BN * 8; i += 32) {      // 8 x 16 B per 128 B row
+                        *reinterpret_cast<uint4*>(vs + i * 16) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(vs + HALF_BYTES + i * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                }
+                const bool have_next = j + 1 < nmax;
+                const int rk = 2 * j + 2, sk = rk % NSTAGE;
+                if (have_next) {
+                    ok = bounded_wait(bar(B_KVFULL + sk), (rk / NSTAGE) & 1, s_abort, 5, j);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                }
+#pragma unroll
+                for (int t = 0; t < QT; ++t) {
+                    if (j < n_tiles[t]) {
+                        ok = bounded_wait(bar(B_PREADY + t), j & 1, s_abort, 6 + t, j);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        tc_fence_after();
+                        if (lane == 0) {
+                            issue_pv(t, sv, j > 0);
+                            if (j == n_tiles[t] - 1) umma_commit(bar(B_ODONE + t));
+                        }
+                    }
+                    if (j + 1 < n_tiles[t] && lane == 0) {
+                        issue_s(t, sk);
+                        umma_commit(bar(B_SFULL + t));
+                    }
+                }
+                if (!ok) break;
+                if (lane == 0) {
+                    umma_commit(bar(B_KVEMPTY + sv));
+                    if (have_next) umma_commit(bar(B_KVEMPTY + sk));
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax + epilogue
+        const int t = warp >> 2;                       // q tile of this warpgroup
+        const int nt = n_tiles[t];
+        if (nt > 0) {
+            const int row_in_tile = (warp & 3) * 32 + lane;
+            const int row = m0 + t * BM + row_in_tile;     // local row index inside the request
+            const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;
+            const uint32_t tS = tmem_base + lane_base + t * BN;
+            const uint32_t tO = tmem_base + lane_base + QT * BN + t * HD;
+            const float scale = p.scale_log2;
+            float m_run = -INFINITY, l_run = 0.f;
+            bool ok = true;
+            for (int j = 0; j < nt; ++j) {
+                ok = bounded_wait(bar(B_SFULL + t), j & 1, s_abort, 8 + t, j);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t sr[4][32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
+                tmem_wait_ld();
+                const int n0 = j * BN;
+                const int r0 = m0 + t * BM;
+                if (n0 + BN - 1 > r0 - delta || n0 + BN > kv_len) {
+                    const int limit = min(row - delta, kv_len - 1) - n0;     // columns <= limit are visible
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i > limit) sr[c][i] = 0xff800000u;   // -inf
+                }
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[c][i]));
+                const float m_tile = mx * scale;
+                const float m_new = fmaxf(m_run, m_tile);
+                // lazy rescale: keep the old reference maximum unless the row maximum grew by > 2^8
+                const bool need = (m_new > m_run + kRescaleThreshold) || (m_run == -INFINITY && m_new > -INFINITY);
+                float alpha = 1.f;
+                if (need) {
+                    alpha = ex2(m_run - m_new);       // 0 when the row had no key before
+                    l_run *= alpha;
+                    m_run = m_new;
+                }
+                if (j > 0 && __any_sync(0xffffffffu, need)) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t orow[32];
+                        tmem_ld32(tO + c * 32, orow);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                        tmem_st32(tO + c * 32, orow);
+                    }
+                }
+                const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+                float lsum = 0.f;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int col = c * 64 + 2 * i;
+                        const float p0 = ex2(fmaf(__uint_as_float(sr[col >> 5][col & 31]), scale, -m_use));
+                        const float p1 = ex2(fmaf(__uint_as_float(sr[(col + 1) >> 5][(col + 1) & 31]), scale, -m_use));
+                        lsum += p0 + p1;
+                        pk[i] = Cvt<T>::pack(p0, p1);
+                    }
+                    tmem_st32(tS + c * 32, pk);        // P aliases the first 64 columns of S
+                }
+                l_run += lsum;
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar(B_PREADY + t));
+            }
+            if (ok) {
+                ok = bounded_wait(bar(B_ODONE + t), 0, s_abort, 10 + t, nt);
+                ok = __all_sync(0xffffffffu, ok);
+            }
+            if (ok) {
+                tc_fence_after();
+                const bool live = (row < q_len) && (l_run > 0.f);
+                const int64_t grow = (int64_t)q_start + row;
+                float a_old = 0.f, a_new = 0.f, inv_l = 0.f;
+                if (live) {
+                    const int64_t si = grow * p.num_q_heads + head;
+                    const float m_old = p.m[si], l_old = p.l[si];
+                    const float m_new = fmaxf(m_run, m_old);
+                    a_old = l_old * ex2(m_old - m_new);       // 0 for a fresh (-inf, 0) state
+                    a_new = ex2(m_run - m_new);
+                    const float l_new = a_old + l_run * a_new;
+                    inv_l = 1.f / l_new;
+                    p.m[si] = m_new;
+                    p.l[si] = l_new;
+                }
+                OT* orow_g = reinterpret_cast<OT*>(p.o) + grow * p.o_stride_t + (int64_t)head * p.o_stride_h;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t acc[32];
+                    tmem_ld32(tO + c * 32, acc);
+                    tmem_wait_ld();
+                    if (live) {
+                        float x[32];
+                        if (a_old != 0.f) {
+                            load_row32<OT>(orow_g + c * 32, x);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                x[i] = (x[i] * a_old + __uint_as_float(acc[i]) * a_new) * inv_l;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(acc[i]) * (a_new * inv_l);
+                        }
+                        store_row32<OT>(orow_g + c * 32, x);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// [tokens, heads, 128] 16-bit tensor, box = 64 dims x 1 head x 128 tokens, 128-byte swizzle.
+static int make_tile_map(CUtensorMap* tm, const void* base, int64_t tokens, int heads, int64_t stride_t,
+                         int64_t stride_h, int dtype) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) { snprintf(last_cuda_error_buf(), 256, "cuTensorMapEncodeTiled entry point not found"); return ESP_ERR_CUDA; }
+    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)stride_h * 2, (cuuint64_t)stride_t * 2};
+    cuuint32_t box[3] = {64, 1, (cuuint32_t)BN};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(tm, dtype == ESP_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                    3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(last_cuda_error_buf(), 256, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        return ESP_ERR_CUDA;
+    }
+    return ESP_OK;
+}
+
+template <typename T, typename OT>
+static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                          const PrefillParams& pp, dim3 grid, cudaStream_t s) {
+    // set on every launch: the attribute is per device and a process may drive several
+    ESP_CUDA_TRY(cudaFuncSetAttribute(prefill_step_kernel<T, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+    prefill_step_kernel<T, OT><<<grid, NUM_THREADS, SMEM_DYN, s>>>(tq, tk, tv, pp);
+    ESP_LAUNCH_CHECK("prefill_step_kernel");
+    return ESP_OK;
+}
+
+__global__ void state_init_kernel(float* m, float* l, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        m[i] = -INFINITY; l[i] = 0.f;
+    }
+}
+__global__ void lse_kernel(const float* m, const float* l, float* lse, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        lse[i] = l[i] > 0.f ? m[i] * 0.6931471805599453f + logf(l[i]) : -INFINITY;
+}
+
+}  // namespace esp
+
+using namespace esp;
+
+extern "C" int esp_prefill_step(const void* q, int64_t q_stride_t, int64_t q_stride_h, int64_t q_tokens,
+                                const void* k, const void* v, int64_t kv_stride_t, int64_t kv_stride_h,
+                                int64_t kv_tokens, void* o, int64_t o_stride_t, int64_t o_stride_h,
+                                float* m, float* l, const int32_t* q_b_start_loc,
+                                const int32_t* q_b_seq_len, const int32_t* q_first_token_global_idx,
+                                const int32_t* kv_b_start_loc, const int32_t* kv_b_seq_len,
+                                const int32_t* kv_first_token_global_idx, int32_t batch,
+                                int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                int32_t logical_sp_peers_num, int32_t max_q_b_seq_len, int32_t dtype,
+                                int32_t o_dtype, float sm_scale, void* stream) {
+    if (batch == 0 || max_q_b_seq_len <= 0 || q_tokens == 0 || kv_tokens == 0) return ESP_OK;
+    if (!q || !k || !v || !o || !m || !l || !q_b_start_loc || !q_b_seq_len || !q_first_token_global_idx ||
+        !kv_b_start_loc || !kv_b_seq_len || !kv_first_token_global_idx || batch < 0 || num_q_heads <= 0 ||
+        num_kv_heads <= 0 || num_q_heads % num_kv_heads || logical_sp_peers_num <= 0 || q_tokens < 0 ||
+        kv_tokens < 0)
+        return ESP_ERR_BAD_ARG;
+    if (dtype != ESP_DTYPE_F16 && dtype != ESP_DTYPE_BF16) return ESP_ERR_BAD_ARG;
+    if (o_dtype != dtype && o_dtype != ESP_DTYPE_F32) return ESP_ERR_BAD_ARG;
+    if (head_dim != HD) return ESP_ERR_UNSUPPORTED;
+    if (batch > 65535 || num_q_heads > 65535) return ESP_ERR_TOO_LARGE;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || (q_stride_t % 8) ||
+        (q_stride_h % 8) || (kv_stride_t % 8) || (kv_stride_h % 8) || (o_stride_t % 8) || (o_stride_h % 8))
+        return ESP_ERR_ALIGNMENT;
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = make_tile_map(&tq, q, q_tokens, num_q_heads, q_stride_t, q_stride_h, dtype))) return rc;
+    if ((rc = make_tile_map(&tk, k, kv_tokens, num_kv_heads, kv_stride_t, kv_stride_h, dtype))) return rc;
+    if ((rc = make_tile_map(&tv, v, kv_tokens, num_kv_heads, kv_stride_t, kv_stride_h, dtype))) return rc;
+    PrefillParams pp;
+    pp.o = o; pp.m = m; pp.l = l; pp.o_stride_t = o_stride_t; pp.o_stride_h = o_stride_h;
+    pp.q_start = q_b_start_loc; pp.q_len = q_b_seq_len; pp.q_first = q_first_token_global_idx;
+    pp.kv_start = kv_b_start_loc; pp.kv_len = kv_b_seq_len; pp.kv_first = kv_first_token_global_idx;
+    pp.num_q_heads = num_q_heads; pp.group = num_q_heads / num_kv_heads; pp.stride_s = logical_sp_peers_num;
+    pp.num_qblocks = (max_q_b_seq_len + QT * BM - 1) / (QT * BM);
+    pp.scale_log2 = (sm_scale > 0.f ? sm_scale : 1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
+    dim3 grid(pp.num_qblocks, num_q_heads, batch);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == ESP_DTYPE_F16)
+        return o_dtype == ESP_DTYPE_F32 ? launch_prefill<__half, float>(tq, tk, tv, pp, grid, s)
+                                        : launch_prefill<__half, __half>(tq, tk, tv, pp, grid, s);
+    return o_dtype == ESP_DTYPE_F32 ? launch_prefill<__nv_bfloat16, float>(tq, tk, tv, pp, grid, s)
+                                    : launch_prefill<__nv_bfloat16, __nv_bfloat16>(tq, tk, tv, pp, grid, s);
+}
+
+extern "C" int esp_prefill_state_init(void* o, int64_t o_bytes, float* m, float* l,
+                                      int64_t rows_times_heads, void* stream) {
+    if (!m || !l || rows_times_heads < 0 || o_bytes < 0) return ESP_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (o && o_bytes) ESP_CUDA_TRY(cudaMemsetAsync(o, 0, (size_t)o_bytes, s));
+    if (rows_times_heads) {
+        state_init_kernel<<<kNumSMs * 4, 256, 0, s>>>(m, l, rows_times_heads);
+        ESP_LAUNCH_CHECK("state_init_kernel");
+    }
+    return ESP_OK;
+}
+
+extern "C" int esp_prefill_lse(const float* m, const float* l, float* lse, int64_t n, void* stream) {
+    if (n == 0) return ESP_OK;
+    if (!m || !l || !lse || n < 0) return ESP_ERR_BAD_ARG;
+    lse_kernel<<<kNumSMs * 4, 256, 0, (cudaStream_t)stream>>>(m, l, lse, n);
+    ESP_LAUNCH_CHECK("lse_kernel");
+    return ESP_OK;
+}
+
+extern "C" int esp_device_status(int32_t out[4], int32_t clear) {
+    if (!out) return ESP_ERR_BAD_ARG;
+    ESP_CUDA_TRY(cudaDeviceSynchronize());
+    ESP_CUDA_TRY(cudaMemcpyFromSymbol(out, g_esp_status, sizeof(int) * 4));
+    if (clear) {
+        int zero[4] = {0, 0, 0, 0};
+        ESP_CUDA_TRY(cudaMemcpyToSymbol(g_esp_status, zero, sizeof(zero)));
+    }
+    return ESP_OK;
+}

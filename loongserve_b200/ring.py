@@ -1,0 +1,208 @@
+"""Ring prefill loop and multi-master decode exchange: the orchestration around the kernels, following
+loongserve/models/llama/layer_infer/longserve_transformer_layer_infer.py:104-222 (ring) and :224-370
+(multi-master decode).  The communicator is duck-typed (``nccl_group_start/end``, ``nccl_send/recv``,
+``wait_for_default_stream``, ``let_default_stream_wait``) so the same loop runs over
+``loongserve_b200.rnccl.RNCCLComm`` on GPUs and over a gloo-backed stand-in in the CPU tests; the
+attention / scatter callables are injected the same way.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+import torch
+
+
+def shard_lengths(lens: Sequence[int], P: int, striped: bool):
+    """Per logical rank: local token count and first global index of every request.
+    striped = reference placement (token t on rank t mod P, io_struct.py:78-81)."""
+    local_len, first = [], []
+    for r in range(P):
+        ll, ff = [], []
+        for L in lens:
+            L = int(L)
+            if striped:
+                ll.append(max(0, (L - r + P - 1) // P)); ff.append(r)
+            else:
+                per = (L + P - 1) // P
+                b, e = min(L, r * per), min(L, (r + 1) * per)
+                ll.append(e - b); ff.append(b)
+        local_len.append(ll); first.append(ff)
+    return local_len, first, (P if striped else 1)
+
+
+@dataclass
+class BlockMeta:
+    """start_loc / seq_len / first_token_global_idx of one rank's packed KV block (int32 [batch])."""
+    start_loc: torch.Tensor
+    seq_len: torch.Tensor
+    first_idx: torch.Tensor
+
+    @staticmethod
+    def from_lengths(lens, first, device):
+        sl = torch.tensor(lens, dtype=torch.int32)
+        st = torch.cumsum(sl, 0, dtype=torch.int32) - sl
+        return BlockMeta(st.to(device), sl.to(device), torch.tensor(first, dtype=torch.int32).to(device))
+
+
+@dataclass
+class KeepPlan:
+    """Scale-down bookkeeping of one prefill (longserve_transformer_layer_infer.py:180-220): which
+    global token range of every request this instance keeps, the slots to put them in, and the
+    per-ring-step ranges computed at layer 0 and reused by the other layers."""
+    kv_cache_index_begin: torch.Tensor
+    kv_cache_index_end: torch.Tensor
+    mem_index: torch.Tensor
+    b_req_idx: torch.Tensor
+    req_to_token_indexs: torch.Tensor
+    cur_kv_cache_index: torch.Tensor
+    cached: list = field(default_factory=list)
+
+
+def ring_context_attention(q, local_kv, o, m, l, *, rank: int, peers: Sequence[int], metas: Sequence[BlockMeta],
+                           stride: int, max_len_in_batch: int, num_kv_heads: int, comm, recv_buffers,
+                           attention_fn: Callable, init_fn: Callable, overlap: bool = True,
+                           keep: Optional[KeepPlan] = None, pool_layer=None, layer_idx: int = 0,
+                           keep_fns=None):
+    """One layer's ring pass on logical rank ``rank`` of the ring ``peers`` (SP ranks in ring order).
+
+    q [Tq, Hq, D]; local_kv [max_token_num, 2*Hkv, D] (K heads then V heads); ``recv_buffers`` two
+    buffers of local_kv's shape; ``metas[r]`` describes logical rank r's block (a pure function of the
+    request lengths, so it is computed on the host instead of travelling with the block as in the
+    reference, :162-178).  At step i the rank attends to the block of logical rank (rank - i) mod P,
+    sends it on to rank+1 and receives the next one from rank-1 (:163,171).  With ``overlap`` the
+    exchange of block i runs on the communicator's stream while block i is being attended to; without
+    it the exchange is queued behind the kernel as in the reference's default mode (:464-465).
+    """
+    P = len(peers)
+    init_fn(o, m, l)
+    Hkv = num_kv_heads
+    cur = local_kv
+    nxt_rank = peers[(rank + 1) % P]
+    prv_rank = peers[(rank - 1 + P) % P]
+    num_used = 0
+    if keep is not None:
+        keep.cur_kv_cache_index.zero_()
+    for i in range(P):
+        src = (rank - i) % P
+        meta = metas[src]
+        recv = None
+        if i != P - 1:
+            recv = recv_buffers[i % 2]
+            if overlap:
+                comm.wait_for_default_stream()      # block i is ready, the receive buffer is no longer read
+                comm.nccl_group_start()
+                comm.nccl_recv(recv, prv_rank)
+                comm.nccl_send(cur, nxt_rank)
+                comm.nccl_group_end()
+        attention_fn(q, cur[:, :Hkv, :], cur[:, Hkv:, :], o, metas[rank].start_loc, metas[rank].seq_len,
+                     metas[rank].first_idx, meta.start_loc, meta.seq_len, meta.first_idx, stride,
+                     max_len_in_batch, m, l)
+        if i != P - 1 and not overlap:
+            comm.wait_for_default_stream()
+            comm.nccl_group_start()
+            comm.nccl_recv(recv, prv_rank)
+            comm.nccl_send(cur, nxt_rank)
+            comm.nccl_group_end()
+        if keep is not None:
+            pre_fn, copy_fn = keep_fns
+            if layer_idx == 0:
+                rb, re, nl = pre_fn(keep.kv_cache_index_begin, keep.kv_cache_index_end, meta.first_idx, P)
+                nls = torch.cumsum(nl, dim=0, dtype=torch.int64)
+                keep.cached.append((rb, re, nl, nls, int(nls[-1].item())))
+            rb, re, nl, nls, total = keep.cached[i]
+            copy_fn(len(meta.seq_len), nl, rb, re, nls, cur, meta.start_loc, keep.cur_kv_cache_index,
+                    keep.mem_index, pool_layer, keep.req_to_token_indexs, keep.b_req_idx, num_used,
+                    max_len_in_batch + 1, layer_idx == 0)
+            num_used += total
+            if layer_idx == 0:
+                keep.cur_kv_cache_index += nl
+        if i != P - 1:
+            comm.let_default_stream_wait()          # the next block has arrived before it is read
+            cur = recv
+    return o
+
+
+@dataclass
+class MasterPlan:
+    """What a master instance needs for one multi-master decode step
+    (longserve_model.py:505-533, longserve_transformer_layer_infer.py:268-281,312-367)."""
+    peers: Sequence[int]              # SP ranks of all logical peers of this master's batch (incl. itself)
+    b_req_idx: torch.Tensor
+    b_seq_len: torch.Tensor           # local lengths on the master (new token included)
+    max_len_in_batch: int
+    block_seq: int
+    global_mid_o: torch.Tensor        # [(P-1) + nblk, B, Hq, D] fp32
+    global_mid_lse: torch.Tensor      # [(P-1) + nblk, B, Hq] fp32
+    global_merge_len: torch.Tensor    # int32 [B] = (P-1) + ceil(len / block_seq)
+    global_out_lse: torch.Tensor      # fp32 [B, Hq]
+
+
+@dataclass
+class PeerPlan:
+    """What an instance needs to serve other masters' queries in the same step (pre_process.py:194-230)."""
+    masters: Sequence[int]            # SP ranks of the other masters, logical order
+    ranges: Sequence[tuple]           # slice of peer_query_buffer belonging to each of them
+    peer_query_buffer: torch.Tensor   # [peer_bs, Hq, D]
+    peer_b_req_idx: torch.Tensor
+    peer_b_seq_len: torch.Tensor      # local token counts of the foreign requests
+    peer_max_len_in_batch: int
+    block_seq: int
+    peer_mid_o: torch.Tensor
+    peer_mid_lse: torch.Tensor
+    peer_o: torch.Tensor              # fp32 [peer_bs, Hq, D]
+    peer_lse: torch.Tensor            # fp32 [peer_bs, Hq]
+
+
+def multi_master_decode_attention(q, pool_layer, req_to_token_indexs, num_kv_heads: int, comm, my_rank: int,
+                                  master: Optional[MasterPlan], peer: Optional[PeerPlan], stage1_fn: Callable,
+                                  stage2_fn: Callable, out=None):
+    """One layer of multi-master distributed decode attention on one instance
+    (longserve_transformer_layer_infer.py:224-370): queries travel to the instances holding the KV,
+    partial (o fp32, lse) come back, the master merges them with its own split-KV partials."""
+    Hkv = num_kv_heads
+    k_cache, v_cache = pool_layer[:, :Hkv, :], pool_layer[:, Hkv:, :]
+    if master is not None:
+        comm.wait_for_default_stream()
+    comm.nccl_group_start()
+    if peer is not None:
+        for mrank, (b0, b1) in zip(peer.masters, peer.ranges):
+            comm.nccl_recv(peer.peer_query_buffer[b0:b1], mrank)
+    if master is not None:
+        for prank in master.peers:
+            if prank != my_rank:
+                comm.nccl_send(q, prank)
+    comm.nccl_group_end()
+
+    n_other = 0
+    if master is not None:
+        n_other = len(master.peers) - 1
+        stage1_fn(master.global_mid_o[n_other:], master.global_mid_lse[n_other:], q, k_cache, v_cache,
+                  req_to_token_indexs, master.b_req_idx, master.b_seq_len, master.max_len_in_batch, master.block_seq)
+    if peer is not None:
+        comm.let_default_stream_wait()
+        stage1_fn(peer.peer_mid_o, peer.peer_mid_lse, peer.peer_query_buffer, k_cache, v_cache,
+                  req_to_token_indexs, peer.peer_b_req_idx, peer.peer_b_seq_len, peer.peer_max_len_in_batch,
+                  peer.block_seq)
+        stage2_fn(peer.peer_o, peer.peer_lse, peer.peer_b_seq_len, peer.peer_mid_o, peer.peer_mid_lse, peer.block_seq)
+        comm.wait_for_default_stream()
+
+    comm.nccl_group_start()
+    if master is not None:
+        others = [r for r in master.peers if r != my_rank]
+        for i, prank in enumerate(others):
+            comm.nccl_recv(master.global_mid_o[i], prank)
+            comm.nccl_recv(master.global_mid_lse[i], prank)
+    if peer is not None:
+        for mrank, (b0, b1) in zip(peer.masters, peer.ranges):
+            comm.nccl_send(peer.peer_o[b0:b1], mrank)
+            comm.nccl_send(peer.peer_lse[b0:b1], mrank)
+    comm.nccl_group_end()
+
+    o_tensor = None
+    comm.let_default_stream_wait()
+    if master is not None:
+        o_tensor = torch.empty_like(q) if out is None else out
+        stage2_fn(o_tensor, master.global_out_lse, master.global_merge_len, master.global_mid_o,
+                  master.global_mid_lse, 1)
+    return o_tensor

@@ -1,0 +1,184 @@
+"""Host-side logic on CPU: the pool managers against the reference-generated golden trace, and the ring /
+multi-master orchestration run as world_size-2 gloo processes with the CPU oracle standing in for the
+kernels (BASELINE correctness configuration: one 4096-token sequence, 2 contiguous shards of 2048,
+32 q/kv heads x 128, fp32, seed 0)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import esp_oracle as O
+
+
+def test_mem_manager_matches_reference_trace(golden_dir):
+    from loongserve_b200.mem_manager import LongServeMemoryManager, LongServeReqManager
+    g = np.load(os.path.join(golden_dir, "mem_manager.npz"))
+    mm = LongServeMemoryManager(64, torch.float16, 2, 8, 1, device="cpu")
+    a = mm.alloc(5)
+    assert np.array_equal(a.numpy(), g["t0_alloc5"]) and mm.can_use_mem_size == int(g["t0_free"])
+    b = mm.alloc_contiguous(7)
+    assert np.array_equal(b[0].numpy(), g["t1_contig7"]) and mm.can_use_mem_size == int(g["t1_free"])
+    mm.free(a[1:4])
+    assert np.array_equal(mm.mem_state.numpy(), g["t2_free_a1_4"]) and mm.can_use_mem_size == int(g["t2_free"])
+    c = mm.alloc(6)
+    assert np.array_equal(c.numpy(), g["t3_alloc6"]) and mm.can_use_mem_size == int(g["t3_free"])
+    d = mm.alloc_contiguous(4)
+    assert np.array_equal(d[0].numpy(), g["t4_contig4"]) and mm.can_use_mem_size == int(g["t4_free"])
+    mm.add_refs(c[:2])
+    assert np.array_equal(mm.mem_state.numpy(), g["t5_addref"]) and mm.can_use_mem_size == int(g["t5_free"])
+    mm.free(c)
+    assert np.array_equal(mm.mem_state.numpy(), g["t6_free_c"]) and mm.can_use_mem_size == int(g["t6_free"])
+    assert mm.alloc_contiguous(60) is None
+    with pytest.raises(RuntimeError):
+        mm.alloc(10_000)
+    assert mm.kv_buffer.shape == (1, 64, 4, 8)
+    rm = LongServeReqManager(4, 16, mm)
+    assert int(rm.req_to_token_indexs[0, 0]) == 2147483647
+    idx = rm.alloc(3)
+    assert idx.tolist() == [0, 1, 2] and rm.can_use_req_size == 1 and rm.alloc(2) is None
+    rm.free(idx[:1], None)
+    assert rm.alloc(1).tolist() == [0]
+
+
+class GlooComm:
+    """CPU stand-in with RNCCLComm's surface: grouped point-to-point over gloo."""
+
+    def __init__(self):
+        self.ops = []
+
+    def nccl_group_start(self):
+        self.ops = []
+
+    def nccl_send(self, t, peer):
+        if t.numel():
+            self.ops.append(dist.P2POp(dist.isend, t.contiguous(), peer))
+
+    def nccl_recv(self, t, peer):
+        if t.numel():
+            assert t.is_contiguous()
+            self.ops.append(dist.P2POp(dist.irecv, t, peer))
+
+    def nccl_group_end(self):
+        if self.ops:
+            for w in dist.batch_isend_irecv(self.ops):
+                w.wait()
+        self.ops = []
+
+    def wait_for_default_stream(self):
+        pass
+
+    def let_default_stream_wait(self):
+        pass
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
+
+
+def _ring_worker(rank, world, port, striped, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from loongserve_b200 import ring
+    torch.manual_seed(0)
+    T, Hh, D = 4096, 32, 128
+    q = torch.randn(T, Hh, D); k = torch.randn(T, Hh, D); v = torch.randn(T, Hh, D)
+    lens = [T]
+    local_len, first, stride = ring.shard_lengths(lens, world, striped)
+    qs = O.shard_tokens(q, lens, world, striped)[rank]
+    kv = torch.cat([O.shard_tokens(k, lens, world, striped)[rank], O.shard_tokens(v, lens, world, striped)[rank]], dim=1)
+    metas = [ring.BlockMeta.from_lengths(local_len[r], first[r], "cpu") for r in range(world)]
+    o = torch.empty_like(qs); m = torch.empty(qs.shape[0], Hh); l = torch.empty(qs.shape[0], Hh)
+
+    def init_fn(o_, m_, l_):
+        o_.zero_(); m_.fill_(float("-inf")); l_.zero_()
+
+    def attn(q_, k_, v_, o_, qs_, ql_, qf_, ks_, kl_, kf_, s_, mx_, m_, l_):
+        O.ring_step(q_, k_, v_, o_, m_, l_, qs_, ql_, qf_, ks_, kl_, kf_, s_)
+
+    ring.ring_context_attention(qs, kv, o, m, l, rank=rank, peers=list(range(world)), metas=metas, stride=stride,
+                                max_len_in_batch=qs.shape[0], num_kv_heads=Hh, comm=GlooComm(),
+                                recv_buffers=[torch.empty_like(kv), torch.empty_like(kv)], attention_fn=attn, init_fn=init_fn)
+    torch.save((o, O.lse_from_state(m, l)), os.path.join(out, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("striped", [False, True])
+def test_ring_world2_gloo_equals_full_attention(tmp_path, striped):
+    world = 2
+    mp.spawn(_ring_worker, args=(world, _free_port(), striped, str(tmp_path)), nprocs=world, join=True)
+    torch.manual_seed(0)
+    T, Hh, D = 4096, 32, 128
+    q = torch.randn(T, Hh, D); k = torch.randn(T, Hh, D); v = torch.randn(T, Hh, D)
+    ro, rlse = O.full_causal_attention(q, k, v, [T])
+    parts = [torch.load(os.path.join(str(tmp_path), f"r{r}.pt")) for r in range(world)]
+    o = O.unshard_tokens([p[0] for p in parts], [T], world, striped)
+    lse = O.unshard_tokens([p[1] for p in parts], [T], world, striped)
+    assert torch.allclose(o, ro, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(lse, rlse, atol=1e-4, rtol=1e-5)
+
+
+def _decode_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from loongserve_b200 import ring
+    g = torch.Generator().manual_seed(0)
+    B, Hh, D, bs = 4, 8, 128, 64
+    lens = [300, 41, 129, 64]
+    total = sum(lens)
+    kall = torch.randn(total, Hh, D, generator=g); vall = torch.randn(total, Hh, D, generator=g)
+    q = torch.randn(B, Hh, D, generator=g)
+    # token t of request b lives on instance (t mod world); instance 0 is the only master
+    pool = torch.zeros(total, 2 * Hh, D); rt = torch.full((B, 400), O.INT32_MAX, dtype=torch.int32)
+    loc_len = []
+    off = 0; slot = 0
+    for b, L in enumerate(lens):
+        mine = list(range(rank, L, world))
+        for j, t in enumerate(mine):
+            pool[slot, :Hh] = kall[off + t]; pool[slot, Hh:] = vall[off + t]; rt[b, j] = slot; slot += 1
+        loc_len.append(len(mine)); off += L
+    b_req = torch.arange(B, dtype=torch.int32); b_len = torch.tensor(loc_len, dtype=torch.int32)
+    mx = max(loc_len); nblk = (mx + bs - 1) // bs
+    master = peer = None
+    if rank == 0:
+        master = ring.MasterPlan(peers=list(range(world)), b_req_idx=b_req, b_seq_len=b_len, max_len_in_batch=mx, block_seq=bs,
+                                 global_mid_o=torch.zeros(world - 1 + nblk, B, Hh, D), global_mid_lse=torch.zeros(world - 1 + nblk, B, Hh),
+                                 global_merge_len=(world - 1 + (b_len + bs - 1) // bs).to(torch.int32),
+                                 global_out_lse=torch.zeros(B, Hh))
+    else:
+        peer = ring.PeerPlan(masters=[0], ranges=[(0, B)], peer_query_buffer=torch.zeros(B, Hh, D), peer_b_req_idx=b_req,
+                             peer_b_seq_len=b_len, peer_max_len_in_batch=mx, block_seq=bs,
+                             peer_mid_o=torch.zeros(nblk, B, Hh, D), peer_mid_lse=torch.zeros(nblk, B, Hh),
+                             peer_o=torch.zeros(B, Hh, D), peer_lse=torch.zeros(B, Hh))
+
+    def s1(mid_o, mid_l, q_, k_, v_, rt_, br_, bl_, mx_, bs_):
+        O.flash_decoding_stage1(mid_o, mid_l, q_, k_, v_, rt_, br_, bl_, mx_, bs_)
+
+    def s2(o_, lse_, bl_, mid_o, mid_l, bs_):
+        O.flash_decoding_stage2(o_, lse_, bl_, mid_o, mid_l, bs_)
+
+    o = ring.multi_master_decode_attention(q if rank == 0 else None, pool, rt, Hh, GlooComm(), rank, master, peer, s1, s2)
+    if rank == 0:
+        torch.save((o, master.global_out_lse), os.path.join(out, "dec.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_multi_master_decode_world2_gloo(tmp_path):
+    world = 2
+    mp.spawn(_decode_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    o, lse = torch.load(os.path.join(str(tmp_path), "dec.pt"))
+    g = torch.Generator().manual_seed(0)
+    B, Hh, D = 4, 8, 128
+    lens = [300, 41, 129, 64]; total = sum(lens)
+    kall = torch.randn(total, Hh, D, generator=g); vall = torch.randn(total, Hh, D, generator=g)
+    q = torch.randn(B, Hh, D, generator=g)
+    rt = torch.full((B, 400), O.INT32_MAX, dtype=torch.int32); off = 0
+    for b, L in enumerate(lens):
+        rt[b, :L] = torch.arange(off, off + L, dtype=torch.int32); off += L
+    ro, rl = O.token_decode_attention(q, kall, vall, rt, torch.arange(B, dtype=torch.int32), torch.tensor(lens, dtype=torch.int32))
+    assert torch.allclose(o, ro, atol=1e-5, rtol=1e-5) and torch.allclose(lse, rl, atol=1e-5, rtol=1e-5)
