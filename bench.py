@@ -143,12 +143,11 @@ def run_reference_arm(args):
 
 
 # ------------------------------------------------------------------------------------------------
-def decode_bench(torch, peaks, steps=10, warmup=3):
+def decode_bench(torch, peaks, steps=10, warmup=3, B=64):
     """Distributed flash-decoding on one instance: stage 1 + merge over a shuffled token-indexed pool."""
     from loongserve_b200 import flash_decoding as fd
     dev = "cuda"
     g = torch.Generator().manual_seed(0)
-    B = 64
     lens = torch.randint(4096, 65537, (B,), generator=g)
     total = int(lens.sum())
     pool = torch.empty(total + 8, 2 * H, D, dtype=torch.bfloat16, device=dev)
@@ -190,7 +189,7 @@ def decode_bench(torch, peaks, steps=10, warmup=3):
     out = {"metric": "decode_attention_hbm_gbs", "value": gbs, "unit": "GB/s", "stage1_ms": t1, "merge_ms": t2,
            "stage1_plus_merge_gbs": alg_bytes / ((t1 + t2) * 1e-3) / 1e9,
            "config": {"workload": f"batch {B} x U[4096,65536] tokens ({total} total), {H}x{D} bf16, shuffled token-indexed pool, split {bs}",
-                      "l2": "pool (36 GB) far larger than L2"},
+                      "l2": f"pool ({total * 2 * H * D * 2 / 1e9:.1f} GB) far larger than L2"},
            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
                         "traffic": None, "peak_source": peaks["src"]},
            "algorithmic_bytes": alg_bytes, "gpu_launches_per_step": 2}
@@ -230,9 +229,16 @@ def main():
     ap.add_argument("--layout", default="striped", choices=["striped", "contiguous"])
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--skip-extras", action="store_true", help="skip e2e / decode / cpu baseline (profiling runs)")
+    ap.add_argument("--decode-only", action="store_true", help="run only the decode part (profiling runs)")
+    ap.add_argument("--decode-batch", type=int, default=64)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.decode_only:
+        import torch
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        print(json.dumps(decode_bench(torch, load_peaks(), steps=args.steps, warmup=args.warmup, B=args.decode_batch)), flush=True)
         return
 
     import torch

@@ -1,0 +1,167 @@
+"""Two-GPU runs of the ring prefill and of multi-master decode over the raw NCCL layer, one child process
+per GPU, checked against the CPU oracle.  Skipped when fewer than two GPUs are visible."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from oracle import esp_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
+
+
+def _setup(rank, world, port):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)       # host-side rendezvous only
+    from loongserve_b200 import rnccl
+    obj = [rnccl.get_nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(obj, 0)
+    return dist, rnccl.RNCCLComm(obj[0], world, rank)
+
+
+def _ring_worker(rank, world, port, striped, overlap, out):
+    dist, comm = _setup(rank, world, port)
+    from loongserve_b200 import context_attention as ca
+    from loongserve_b200 import kv_ops, ring
+    dev = torch.device("cuda", rank)
+    g = torch.Generator().manual_seed(0)
+    lens = [3000, 77, 1025]
+    T, Hq, Hkv, D = sum(lens), 8, 4, 128
+    q = torch.randn(T, Hq, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+    local_len, first, stride = ring.shard_lengths(lens, world, striped)
+    max_tok = max(sum(x) for x in local_len)
+    qs = O.shard_tokens(q, lens, world, striped)[rank].to(dev)
+    kv = torch.full((max_tok, 2 * Hkv, D), float("nan"), dtype=torch.bfloat16)
+    kr = O.shard_tokens(k, lens, world, striped)[rank]; vr = O.shard_tokens(v, lens, world, striped)[rank]
+    kv[:kr.shape[0], :Hkv] = kr; kv[:vr.shape[0], Hkv:] = vr
+    kv = kv.to(dev)
+    metas = [ring.BlockMeta.from_lengths(local_len[r], first[r], dev) for r in range(world)]
+    o = torch.empty_like(qs); m = torch.empty(qs.shape[0], Hq, device=dev); l = torch.empty(qs.shape[0], Hq, device=dev)
+    # scale-down bookkeeping: rank 0 keeps the first half of every request, rank 1 the rest
+    pool = torch.zeros(T + 16, 2 * Hkv, D, dtype=torch.bfloat16, device=dev)
+    cb = torch.tensor([0 if rank == 0 else L // 2 for L in lens], dtype=torch.int32, device=dev)
+    ce = torch.tensor([L // 2 if rank == 0 else L for L in lens], dtype=torch.int32, device=dev)
+    n_keep = int((ce - cb).sum())
+    gk = torch.Generator().manual_seed(5 + rank)
+    keep = ring.KeepPlan(cb, ce, torch.randperm(T + 16, generator=gk)[:n_keep].to(dev), torch.arange(len(lens), dtype=torch.int32, device=dev),
+                         torch.full((len(lens), 4000), O.INT32_MAX, dtype=torch.int32, device=dev),
+                         torch.zeros(len(lens), dtype=torch.int32, device=dev))
+    ring.ring_context_attention(qs, kv, o, m, l, rank=rank, peers=list(range(world)), metas=metas, stride=stride,
+                                max_len_in_batch=max(local_len[rank]), num_kv_heads=Hkv, comm=comm,
+                                recv_buffers=[torch.empty_like(kv), torch.empty_like(kv)],
+                                attention_fn=ca.context_attention_fwd, init_fn=ca.init_attention_state, overlap=overlap,
+                                keep=keep if striped else None, pool_layer=pool, layer_idx=0,
+                                keep_fns=(kv_ops.pre_copy_and_register_kv, kv_ops.destindex_copy_and_register_kv))
+    torch.cuda.synchronize()
+    st = ca.device_status()
+    torch.save(dict(o=o.cpu(), lse=ca.attention_lse(m, l).cpu(), status=st, pool=pool.cpu(), rtt=keep.req_to_token_indexs.cpu(),
+                    cb=cb.cpu(), ce=ce.cpu()), os.path.join(out, f"r{rank}.pt"))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("striped,overlap", [(True, True), (False, True), (True, False)])
+def test_ring_two_gpus(tmp_path, striped, overlap):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    mp.spawn(_ring_worker, args=(world, _free_port(), striped, overlap, str(tmp_path)), nprocs=world, join=True)
+    g = torch.Generator().manual_seed(0)
+    lens = [3000, 77, 1025]
+    T, Hq, Hkv, D = sum(lens), 8, 4, 128
+    q = torch.randn(T, Hq, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+    ro, rlse = O.full_causal_attention(q, k, v, lens)
+    parts = [torch.load(os.path.join(str(tmp_path), f"r{r}.pt")) for r in range(world)]
+    assert all(p["status"][0] == 0 for p in parts)
+    o = O.unshard_tokens([p["o"] for p in parts], lens, world, striped)
+    lse = O.unshard_tokens([p["lse"] for p in parts], lens, world, striped)
+    assert bool(((o.float() - ro).abs() <= 2e-2 + 1e-2 * ro.abs()).all())
+    assert torch.allclose(lse, rlse, atol=1e-3, rtol=1e-3)
+    if striped:
+        # every instance kept exactly its assigned global range of every request, bit-exact
+        kvfull = torch.cat([k, v], dim=1)
+        starts = [0, lens[0], lens[0] + lens[1]]
+        for r, p in enumerate(parts):
+            for b, L in enumerate(lens):
+                cb, ce = int(p["cb"][b]), int(p["ce"][b])
+                slots = p["rtt"][b, :ce - cb].long()
+                got = p["pool"][slots]
+                want_set = kvfull[starts[b] + cb:starts[b] + ce]
+                # slot order is grouped by ring step (source rank), not by position: compare as multisets of rows
+                key = lambda t: sorted(map(bytes, t.reshape(t.shape[0], -1).view(torch.uint8).numpy()))
+                assert key(got) == key(want_set), f"rank {r} request {b}"
+
+
+def _decode_worker(rank, world, port, out):
+    dist, comm = _setup(rank, world, port)
+    from loongserve_b200 import flash_decoding as fd
+    from loongserve_b200 import ring
+    dev = torch.device("cuda", rank)
+    g = torch.Generator().manual_seed(0)
+    B, Hh, D, bs = 4, 8, 128, 256
+    lens = [3000, 41, 1290, 640]
+    total = sum(lens)
+    kall = torch.randn(total, Hh, D, generator=g).to(torch.bfloat16); vall = torch.randn(total, Hh, D, generator=g).to(torch.bfloat16)
+    q = torch.randn(B, Hh, D, generator=g).to(torch.bfloat16).to(dev)
+    pool = torch.zeros(total, 2 * Hh, D, dtype=torch.bfloat16); rt = torch.full((B, 4000), O.INT32_MAX, dtype=torch.int32)
+    loc_len = []
+    off = 0; slot = 0
+    for b, L in enumerate(lens):
+        mine = list(range(rank, L, world))
+        pool[slot:slot + len(mine), :Hh] = kall[off + rank:off + L:world]
+        pool[slot:slot + len(mine), Hh:] = vall[off + rank:off + L:world]
+        rt[b, :len(mine)] = torch.arange(slot, slot + len(mine), dtype=torch.int32)
+        slot += len(mine); loc_len.append(len(mine)); off += L
+    pool, rt = pool.to(dev), rt.to(dev)
+    b_req = torch.arange(B, dtype=torch.int32, device=dev); b_len = torch.tensor(loc_len, dtype=torch.int32, device=dev)
+    mx = max(loc_len); nblk = (mx + bs - 1) // bs
+    master = peer = None
+    f32 = dict(dtype=torch.float32, device=dev)
+    if rank == 0:
+        master = ring.MasterPlan(peers=list(range(world)), b_req_idx=b_req, b_seq_len=b_len, max_len_in_batch=mx, block_seq=bs,
+                                 global_mid_o=torch.zeros(world - 1 + nblk, B, Hh, D, **f32), global_mid_lse=torch.zeros(world - 1 + nblk, B, Hh, **f32),
+                                 global_merge_len=(world - 1 + (b_len + bs - 1) // bs).to(torch.int32), global_out_lse=torch.zeros(B, Hh, **f32))
+    else:
+        peer = ring.PeerPlan(masters=[0], ranges=[(0, B)], peer_query_buffer=torch.zeros(B, Hh, D, dtype=torch.bfloat16, device=dev),
+                             peer_b_req_idx=b_req, peer_b_seq_len=b_len, peer_max_len_in_batch=mx, block_seq=bs,
+                             peer_mid_o=torch.zeros(nblk, B, Hh, D, **f32), peer_mid_lse=torch.zeros(nblk, B, Hh, **f32),
+                             peer_o=torch.zeros(B, Hh, D, **f32), peer_lse=torch.zeros(B, Hh, **f32))
+    o = ring.multi_master_decode_attention(q if rank == 0 else None, pool, rt, Hh, comm, rank, master, peer,
+                                           fd.flash_decoding_stage1, fd.flash_decoding_stage2)
+    torch.cuda.synchronize()
+    if rank == 0:
+        torch.save((o.cpu(), master.global_out_lse.cpu()), os.path.join(out, "dec.pt"))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+
+
+def test_multi_master_decode_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    mp.spawn(_decode_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    o, lse = torch.load(os.path.join(str(tmp_path), "dec.pt"))
+    g = torch.Generator().manual_seed(0)
+    B, Hh, D = 4, 8, 128
+    lens = [3000, 41, 1290, 640]; total = sum(lens)
+    kall = torch.randn(total, Hh, D, generator=g).to(torch.bfloat16); vall = torch.randn(total, Hh, D, generator=g).to(torch.bfloat16)
+    q = torch.randn(B, Hh, D, generator=g).to(torch.bfloat16)
+    rt = torch.full((B, 4000), O.INT32_MAX, dtype=torch.int32); off = 0
+    for b, L in enumerate(lens):
+        rt[b, :L] = torch.arange(off, off + L, dtype=torch.int32); off += L
+    ro, rl = O.token_decode_attention(q, kall, vall, rt, torch.arange(B, dtype=torch.int32), torch.tensor(lens, dtype=torch.int32))
+    assert torch.allclose(o.float(), ro, atol=2e-2, rtol=1e-2) and torch.allclose(lse, rl, atol=1e-3, rtol=1e-3)
