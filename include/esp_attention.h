@@ -108,6 +108,25 @@ int esp_decode_merge(void* o, float* out_lse, const int32_t* b_seqlen, const flo
                      const float* mid_lse, int32_t batch, int32_t num_heads, int32_t head_dim,
                      int32_t num_blocks, int32_t block_seq, int32_t o_dtype, void* stream);
 
+/* esp_decode_attention_noalloc has no counterpart in the reference.  It is stage 1 + merge in one
+ * call for callers that may not allocate device memory on the serving path (a worker whose whole
+ * memory budget went to the KV cache at start-up, or one replaying a fixed launch sequence): the
+ * per-split partials live in a fixed 16 MiB array inside the library (held by every GPU that loads it,
+ * until the process exits) instead of caller-provided mid_o / mid_lse.  The split size is chosen so the
+ * partials fit; if batch * num_q_heads * (head_dim + 1) floats of a single split exceed the 4 Mi-float
+ * capacity the call returns ESP_ERR_TOO_LARGE and launches nothing.  The call itself performs no
+ * cudaMalloc / cudaFree.  Its first call on a device looks up the array's device address (once per
+ * device, with that device current): make that first call before any stream capture.  Every call on a
+ * device shares the array, so calls that overlap on the GPU race; calls on one stream are safe.
+ * Arguments as esp_decode_stage1 / esp_decode_merge; o_dtype F16/BF16/F32. */
+int esp_decode_attention_noalloc(void* o, float* out_lse, const void* q, const void* k, const void* v,
+                                 int64_t k_stride_t, int64_t k_stride_h, int64_t v_stride_t,
+                                 int64_t v_stride_h, const int32_t* req_to_tokens,
+                                 int64_t req_to_tokens_stride, const int32_t* b_req_idx,
+                                 const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
+                                 int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
+                                 int32_t dtype, int32_t o_dtype, float sm_scale, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Token-indexed KV pool: scatter, registration, migration (all bit-exact copies / integer work).
  * Rows are [heads2, D] with D contiguous; `row_stride` = token stride, `head_stride` = head stride.

@@ -27,6 +27,8 @@ ATTN_SIGNATURES = {
     "esp_decode_stage1": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _vp,
                           _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
     "esp_decode_merge": [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp],
+    "esp_decode_attention_noalloc": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _vp,
+                                     _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
     "esp_kv_scatter": [_vp, _i64, _i64, _vp, _i64, _i64, _vp, _i32, _i64, _i32, _i32, _i32, _vp],
     "esp_kv_keep_range": [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp],
     "esp_kv_scatter_register": [_i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i32, _vp, _i64,

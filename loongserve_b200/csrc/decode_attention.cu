@@ -325,3 +325,80 @@ extern "C" int esp_decode_merge(void* o, float* out_lse, const int32_t* b_seqlen
     ESP_LAUNCH_CHECK("decode_merge_kernel");
     return ESP_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc on the serving path: a worker whose memory pool was
+// sized once at start-up and handed over entirely to the KV cache, or a caller replaying a fixed launch
+// sequence that must not touch the allocator.  The split-KV decode needs scratch for the per-split
+// partial (o, lse) between its two kernels; here that scratch is a fixed array inside the library image,
+// so the call needs nothing beyond its inputs and outputs.
+//
+// Capacity: kNoAllocScratchFloats fp32 values (16 MiB), resident on every GPU that loads the library for
+// the life of the process.  The split size is chosen so the partials fit; a batch whose single split
+// already exceeds the capacity (batch * q heads * 129 > capacity) is rejected with ESP_ERR_TOO_LARGE.
+// All calls on a device share the array: two calls that overlap on the GPU (different streams) race.
+// Nothing needs clearing between calls: stage 1 writes every partial that the merge later reads.
+constexpr long long kNoAllocScratchFloats = 4ll * 1024 * 1024;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+
+namespace esp {
+constexpr int kMaxDevices = 64;
+// Device addresses of g_noalloc_scratch, one per device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel can use; the address comes from the runtime, once per
+// device, with that device current.
+static float* g_noalloc_addr[kMaxDevices] = {nullptr};
+
+static int noalloc_scratch(float** out) {
+    int dev = -1;
+    ESP_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return ESP_ERR_UNSUPPORTED;
+    float* p = g_noalloc_addr[dev];
+    if (!p) {
+        ESP_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch));
+        g_noalloc_addr[dev] = p;      // racing host threads would store the same value
+    }
+    *out = p;
+    return ESP_OK;
+}
+}  // namespace esp
+
+extern "C" int esp_decode_attention_noalloc(void* o, float* out_lse, const void* q, const void* k,
+                                            const void* v, int64_t k_stride_t, int64_t k_stride_h,
+                                            int64_t v_stride_t, int64_t v_stride_h,
+                                            const int32_t* req_to_tokens, int64_t req_to_tokens_stride,
+                                            const int32_t* b_req_idx, const int32_t* b_seqlen,
+                                            int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                            int32_t head_dim, int32_t max_len_in_batch, int32_t dtype,
+                                            int32_t o_dtype, float sm_scale, void* stream) {
+    if (batch == 0) return ESP_OK;
+    if (!o || !out_lse || !q || !k || !v || !req_to_tokens || !b_req_idx || !b_seqlen || batch < 0 ||
+        num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads || max_len_in_batch < 0)
+        return ESP_ERR_BAD_ARG;
+    if (head_dim != 128) return ESP_ERR_UNSUPPORTED;
+    const long long per_split = (long long)batch * num_q_heads * (head_dim + 1);
+    if (per_split > kNoAllocScratchFloats) {
+        snprintf(last_cuda_error_buf(), 256,
+                 "esp_decode_attention_noalloc: batch*heads*(D+1) = %lld floats per split exceeds the fixed scratch of %lld floats",
+                 per_split, kNoAllocScratchFloats);
+        return ESP_ERR_TOO_LARGE;
+    }
+    const int max_len = max_len_in_batch > 0 ? max_len_in_batch : 1;
+    const long long max_splits = kNoAllocScratchFloats / per_split;
+    long long bs = (max_len + max_splits - 1) / max_splits;
+    if (bs < 256) bs = 256;
+    bs = (bs + 255) / 256 * 256;
+    const int nblk = (int)((max_len + bs - 1) / bs);
+    float* scratch = nullptr;
+    int rc = noalloc_scratch(&scratch);
+    if (rc) return rc;
+    float* mid_o = scratch;
+    float* mid_lse = scratch + (long long)nblk * batch * num_q_heads * head_dim;
+    rc = esp_decode_stage1(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t, v_stride_h, req_to_tokens,
+                           req_to_tokens_stride, b_req_idx, b_seqlen, batch, num_q_heads, num_kv_heads, head_dim,
+                           max_len, (int32_t)bs, dtype, sm_scale, stream);
+    if (rc) return rc;
+    return esp_decode_merge(o, out_lse, b_seqlen, mid_o, mid_lse, batch, num_q_heads, head_dim, nblk, (int32_t)bs,
+                            o_dtype, stream);
+}
