@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-ATTN_LIB = os.path.join(HERE, "libesp_attention.so")
+# ESP_ATTENTION_LIB may point at another build of the same library (kernel tuning experiments)
+ATTN_LIB = os.environ.get("ESP_ATTENTION_LIB") or os.path.join(HERE, "libesp_attention.so")
 RNCCL_LIB = os.path.join(HERE, "libesp_rnccl.so")
 
 ESP_DTYPE_F16, ESP_DTYPE_BF16, ESP_DTYPE_F32 = 0, 1, 2

@@ -4,7 +4,7 @@
 // One CTA owns 256 consecutive q rows of one (request, head) as two 128-row tiles.  Warp roles:
 //   warps 0-3  softmax of tile 0 (one thread per row), warps 4-7 softmax of tile 1,
 //   warp 8     TMA producer (Q tiles once, then K_0 V_0 K_1 V_1 ... through a ring of 32 KiB stages),
-//   warp 9     tcgen05.mma issuer and owner of the tensor-memory allocation.
+//   warp 9     tcgen05.mma issuer and owner of the tensor-memory allocation; warps 10-11 only lend registers.
 // Per kv tile and q tile:  S = Q K^T (tcgen05.mma, both operands K-major in 128B-swizzled smem, fp32
 // accumulator in tensor memory) -> softmax threads read their row with tcgen05.ld, apply the mask only
 // on diagonal/tail tiles, keep a running base-2 maximum with lazy rescaling of O, write P as packed
@@ -30,7 +30,17 @@ constexpr int HD = 128;               // head dim
 constexpr int NSTAGE = 4;             // K/V ring stages
 constexpr int TILE_BYTES = BN * HD * 2;
 constexpr int HALF_BYTES = TILE_BYTES / 2;   // 64 head-dim columns x 128 rows (one swizzle-128B panel)
-constexpr int NUM_THREADS = 320;
+#ifndef ESP_PREFILL_THREADS
+#define ESP_PREFILL_THREADS 384       // 3 warpgroups: softmax tile 0, softmax tile 1, {producer, MMA, 2 idle warps}
+#endif
+#ifndef ESP_POLY_EXP_PER_32
+#define ESP_POLY_EXP_PER_32 0         // of every 32 exponentials, this many run on the FMA pipe instead of MUFU
+#endif
+constexpr int NUM_THREADS = ESP_PREFILL_THREADS;
+constexpr bool kUseSetMaxNReg = (NUM_THREADS == 384);
+constexpr int kPolyPer32 = ESP_POLY_EXP_PER_32;
+static_assert(kPolyPer32 == 0 || kPolyPer32 == 2 || kPolyPer32 == 4 || kPolyPer32 == 8 || kPolyPer32 == 16 || kPolyPer32 == 32,
+              "ESP_POLY_EXP_PER_32 must be 0 or a power of two up to 32");
 constexpr int TMEM_COLS = 512;
 constexpr long long kWaitLimitCycles = 2000000000LL;   // about a second
 constexpr float kRescaleThreshold = 8.0f;              // lazy O rescale: tolerate 2^8 growth
@@ -46,6 +56,15 @@ constexpr int SMEM_TOTAL = SMEM_MISC + 16;
 constexpr int SMEM_DYN = SMEM_TOTAL + 1024;            // slack to align the base to 1024 B
 
 __device__ int g_esp_status[4];
+
+#ifdef ESP_PREFILL_TRACE
+// Tuning aid, compiled only into experiment builds: per-phase SM clock stamps of one CTA.
+// g_trace[role][iteration][stamp]; role 0/1 = softmax tile 0/1 (lane 0 of its first warp), 2 = MMA issuer.
+__device__ long long g_trace[3][64][8];
+#define ESP_TRACE(role, j, k) do { if (trace_on && (j) < 64) g_trace[role][j][k] = clock64(); } while (0)
+#else
+#define ESP_TRACE(role, j, k) do { } while (0)
+#endif
 
 struct PrefillParams {
     void* o; float* m; float* l;
@@ -126,6 +145,69 @@ template <typename OT> __device__ __forceinline__ void store_row32_16(OT* p, con
 template <> __device__ __forceinline__ void store_row32<__half>(__half* p, const float (&x)[32]) { store_row32_16<__half>(p, x); }
 template <> __device__ __forceinline__ void store_row32<__nv_bfloat16>(__nv_bfloat16* p, const float (&x)[32]) { store_row32_16<__nv_bfloat16>(p, x); }
 
+
+// ---- softmax arithmetic helpers -------------------------------------------------------------------
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// 2^x on the FMA/ALU pipes for x <= ~8 (Cody-Waite split + degree-3 minimax polynomial on [0,1),
+// relative error < 1e-4, below the 16-bit rounding of P).  x is clamped at -126; -inf gives ~0 (2^-126 * p).
+__device__ __forceinline__ float exp2_poly(float x) {
+    x = fmaxf(x, -126.f);
+    float xf;
+    asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(xf) : "f"(x), "f"(12582912.f));   // 1.5 * 2^23: floor(x) lands in the mantissa
+    const float fl = xf - 12582912.f;
+    const float f = x - fl;                                                     // in [0, 1)
+    float pz = fmaf(f, 0.077119089663028717f, 0.227564394474029541f);
+    pz = fmaf(pz, f, 0.695146143436431885f);
+    pz = fmaf(pz, f, 1.0f);
+    return __uint_as_float(__float_as_uint(pz) + (__float_as_uint(xf) << 23));
+}
+
+// max over one 32-column chunk, optionally masked (columns > limit are invisible); four independent
+// chains keep the dependent latency off the critical path
+__device__ __forceinline__ float chunk_max(uint32_t (&r)[32], int col0, int limit, bool masked) {
+    if (masked) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (col0 + i > limit) r[i] = 0xff800000u;
+    }
+    float a[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        a[c] = fmax3(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1]), __uint_as_float(r[8 * c + 2]));
+        a[c] = fmax3(a[c], __uint_as_float(r[8 * c + 3]), __uint_as_float(r[8 * c + 4]));
+        a[c] = fmax3(a[c], __uint_as_float(r[8 * c + 5]), __uint_as_float(r[8 * c + 6]));
+        a[c] = fmaxf(a[c], __uint_as_float(r[8 * c + 7]));
+    }
+    return fmaxf(fmax3(a[0], a[1], a[2]), a[3]);
+}
+
+// p = 2^(s*scale - m) for one 32-column chunk; packs to 16-bit pairs and returns the chunk's row sum
+// (two independent packed accumulators)
+template <typename T, int OFF>
+__device__ __forceinline__ float chunk_exp(const uint32_t (&r)[32], float scale, float neg_m, uint32_t (&pk)[32]) {
+    const float2 sc2 = make_float2(scale, scale), nm2 = make_float2(neg_m, neg_m);
+    float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+    constexpr int kStride = kPolyPer32 > 0 ? 32 / kPolyPer32 : 1;   // every kStride-th pair goes to the FMA pipe
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sc2, nm2);
+        float2 e;
+        if (kPolyPer32 > 0 && ((i / 2) % kStride) == kStride - 1) {
+            e.x = exp2_poly(x.x); e.y = exp2_poly(x.y);
+        } else {
+            e.x = ex2(x.x); e.y = ex2(x.y);
+        }
+        acc[(i / 2) & 1] = __fadd2_rn(acc[(i / 2) & 1], e);
+        pk[OFF + i / 2] = Cvt<T>::pack(e.x, e.y);
+    }
+    const float2 t = __fadd2_rn(acc[0], acc[1]);
+    return t.x + t.y;
+}
+
 // ------------------------------------------------------------------------------------------------
 template <typename T, typename OT>
 __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
@@ -141,6 +223,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
     volatile int* s_skip = reinterpret_cast<volatile int*>(smem_gen + SMEM_MISC + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef ESP_PREFILL_TRACE
+    const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == 9));
+#endif
     const int qb = p.num_qblocks - 1 - (int)blockIdx.x;      // heaviest q block first
     const int head = blockIdx.y, b = blockIdx.z;
     const int kvh = head / p.group;
@@ -188,7 +273,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
 
-    if (warp == 8) {
+    // With 384 threads the third warpgroup (producer, MMA issuer, two idle warps) hands most of its
+    // registers to the two softmax warpgroups; each role changes its budget at the top of its own branch.
+    if (warp >= 8) {
+      if (kUseSetMaxNReg) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
 #pragma unroll
@@ -211,7 +300,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                 tma_load_3d(dst + HALF_BYTES, tm, bar(B_KVFULL + stage), 64, kvh, kv_start + j * BN);
             }
         }
-    } else if (warp == 9) {
+      } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_s = make_idesc(Fmt<T>::kAB, 0, BM, BN);
         constexpr uint32_t idesc_pv = make_idesc(Fmt<T>::kAB, 1, BM, HD);
@@ -273,18 +362,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
 #pragma unroll
                 for (int t = 0; t < QT; ++t) {
                     if (j < n_tiles[t]) {
+                        ESP_TRACE(2, j, t * 4 + 0);
                         ok = bounded_wait(bar(B_PREADY + t), j & 1, s_abort, 6 + t, j);
+                        ESP_TRACE(2, j, t * 4 + 1);
                         ok = __all_sync(0xffffffffu, ok);
                         if (!ok) break;
                         tc_fence_after();
                         if (lane == 0) {
                             issue_pv(t, sv, j > 0);
+                            ESP_TRACE(2, j, t * 4 + 2);
                             if (j == n_tiles[t] - 1) umma_commit(bar(B_ODONE + t));
                         }
                     }
                     if (j + 1 < n_tiles[t] && lane == 0) {
                         issue_s(t, sk);
                         umma_commit(bar(B_SFULL + t));
+                        ESP_TRACE(2, j, t * 4 + 3);
                     }
                 }
                 if (!ok) break;
@@ -295,8 +388,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                 __syncwarp();
             }
         }
+      }
     } else {
         // ------------------------------------------------------------------ softmax + epilogue
+        if (kUseSetMaxNReg) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int t = warp >> 2;                       // q tile of this warpgroup
         const int nt = n_tiles[t];
         if (nt > 0) {
@@ -309,29 +404,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
             float m_run = -INFINITY, l_run = 0.f;
             bool ok = true;
             for (int j = 0; j < nt; ++j) {
+                ESP_TRACE(t, j, 0);
                 ok = bounded_wait(bar(B_SFULL + t), j & 1, s_abort, 8 + t, j);
+                ESP_TRACE(t, j, 1);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 uint32_t sr[4][32];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
+                tmem_ld32(tS, sr[0]);
+                tmem_ld32(tS + 32, sr[1]);
                 tmem_wait_ld();
+                ESP_TRACE(t, j, 2);
+                tmem_ld32(tS + 64, sr[2]);          // second half streams in while the first is reduced
+                tmem_ld32(tS + 96, sr[3]);
                 const int n0 = j * BN;
                 const int r0 = m0 + t * BM;
-                if (n0 + BN - 1 > r0 - delta || n0 + BN > kv_len) {
-                    const int limit = min(row - delta, kv_len - 1) - n0;     // columns <= limit are visible
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (c * 32 + i > limit) sr[c][i] = 0xff800000u;   // -inf
-                }
-                float mx = -INFINITY;
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[c][i]));
+                const bool masked = (n0 + BN - 1 > r0 - delta) || (n0 + BN > kv_len);
+                const int limit = min(row - delta, kv_len - 1) - n0;     // columns <= limit are visible
+                float mx = fmaxf(chunk_max(sr[0], 0, limit, masked), chunk_max(sr[1], 32, limit, masked));
+                tmem_wait_ld();
+                mx = fmax3(mx, chunk_max(sr[2], 64, limit, masked), chunk_max(sr[3], 96, limit, masked));
+                ESP_TRACE(t, j, 3);
                 const float m_tile = mx * scale;
                 const float m_new = fmaxf(m_run, m_tile);
                 // lazy rescale: keep the old reference maximum unless the row maximum grew by > 2^8
@@ -353,25 +446,28 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                         tmem_st32(tO + c * 32, orow);
                     }
                 }
-                const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-                float lsum = 0.f;
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
+                const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+                float lsum;
+                {
                     uint32_t pk[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int col = c * 64 + 2 * i;
-                        const float p0 = ex2(fmaf(__uint_as_float(sr[col >> 5][col & 31]), scale, -m_use));
-                        const float p1 = ex2(fmaf(__uint_as_float(sr[(col + 1) >> 5][(col + 1) & 31]), scale, -m_use));
-                        lsum += p0 + p1;
-                        pk[i] = Cvt<T>::pack(p0, p1);
-                    }
-                    tmem_st32(tS + c * 32, pk);        // P aliases the first 64 columns of S
+                    const float s0 = chunk_exp<T, 0>(sr[0], scale, neg_m, pk);
+                    const float s1 = chunk_exp<T, 16>(sr[1], scale, neg_m, pk);
+                    tmem_st32(tS, pk);                 // P aliases the first 64 columns of S
+                    lsum = s0 + s1;
                 }
+                {
+                    uint32_t pk[32];
+                    const float s2 = chunk_exp<T, 0>(sr[2], scale, neg_m, pk);
+                    const float s3 = chunk_exp<T, 16>(sr[3], scale, neg_m, pk);
+                    tmem_st32(tS + 32, pk);
+                    lsum += s2 + s3;
+                }
+                ESP_TRACE(t, j, 4);
                 l_run += lsum;
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(bar(B_PREADY + t));
+                ESP_TRACE(t, j, 5);
             }
             if (ok) {
                 ok = bounded_wait(bar(B_ODONE + t), 0, s_abort, 10 + t, nt);
@@ -552,6 +648,14 @@ extern "C" int esp_prefill_lse(const float* m, const float* l, float* lse, int64
     ESP_LAUNCH_CHECK("lse_kernel");
     return ESP_OK;
 }
+
+#ifdef ESP_PREFILL_TRACE
+extern "C" int esp_debug_read_trace(long long* out) {
+    ESP_CUDA_TRY(cudaDeviceSynchronize());
+    ESP_CUDA_TRY(cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 3 * 64 * 8));
+    return ESP_OK;
+}
+#endif
 
 extern "C" int esp_device_status(int32_t out[4], int32_t clear) {
     if (!out) return ESP_ERR_BAD_ARG;
