@@ -58,11 +58,12 @@ class ClockSampler:
         self.index = index
         self.proc = None
         self.lines = []
+        self.t_start = 0.0
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -70,7 +71,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def mark_start(self):
+        """Samples taken before this moment (warm-up) are ignored."""
+        self.t_start = time.time()
 
     def stop(self):
         if self.proc is None:
@@ -82,7 +87,10 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        t_end = time.time()
+        for ts, ln in self.lines:
+            if ts < self.t_start or ts > t_end + 0.05:
+                continue
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -198,6 +206,82 @@ def decode_bench(torch, peaks, steps=10, warmup=3, B=64):
     return out
 
 
+def decode_bench_dist(torch, dist, comm, peaks, rank, P, steps=10, warmup=3, B=64):
+    """Distributed flash-decoding over P instances (BASELINE config 3): every request's tokens are split
+    evenly over the instances (token t on instance t mod P), instance 0 is the master.  A step is the
+    whole exchange: q broadcast -> split-KV stage 1 on every instance -> peers merge and send fp32
+    (o, lse) -> master merges.  Returned GB/s = all instances' algorithmic bytes / max-over-ranks time."""
+    from loongserve_b200 import flash_decoding as fd
+    from loongserve_b200 import ring as ringmod
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(4096, 65537, (B,), generator=g)
+    loc = [(int(L) - rank + P - 1) // P for L in lens]
+    total_loc = sum(loc)
+    pool = torch.empty(total_loc + 8, 2 * H, D, dtype=torch.bfloat16, device=dev)
+    gg = torch.Generator(device=dev).manual_seed(1 + rank)
+    chunk = 1 << 16
+    for s_ in range(0, pool.shape[0], chunk):
+        e = min(pool.shape[0], s_ + chunk)
+        pool[s_:e] = torch.randn(e - s_, 2 * H, D, generator=gg, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    mx = max(loc)
+    rt = torch.full((B, mx), 2147483647, dtype=torch.int32)
+    perm = torch.randperm(total_loc, generator=g).to(torch.int32)
+    off = 0
+    for b in range(B):
+        rt[b, :loc[b]] = perm[off:off + loc[b]]; off += loc[b]
+    rt = rt.to(dev)
+    b_req = torch.arange(B, dtype=torch.int32, device=dev)
+    b_len = torch.tensor(loc, dtype=torch.int32, device=dev)
+    bs = int(os.environ.get("ESP_BENCH_DECODE_BLOCK", "2048"))
+    nblk = (mx + bs - 1) // bs
+    f32 = dict(dtype=torch.float32, device=dev)
+    master = peer = None
+    q = None
+    if rank == 0:
+        q = torch.randn(B, H, D, generator=gg, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        master = ringmod.MasterPlan(peers=list(range(P)), b_req_idx=b_req, b_seq_len=b_len, max_len_in_batch=mx, block_seq=bs,
+                                    global_mid_o=torch.empty(P - 1 + nblk, B, H, D, **f32),
+                                    global_mid_lse=torch.empty(P - 1 + nblk, B, H, **f32),
+                                    global_merge_len=(P - 1 + (b_len + bs - 1) // bs).to(torch.int32),
+                                    global_out_lse=torch.empty(B, H, **f32))
+    else:
+        peer = ringmod.PeerPlan(masters=[0], ranges=[(0, B)], peer_query_buffer=torch.empty(B, H, D, dtype=torch.bfloat16, device=dev),
+                                peer_b_req_idx=b_req, peer_b_seq_len=b_len, peer_max_len_in_batch=mx, block_seq=bs,
+                                peer_mid_o=torch.empty(nblk, B, H, D, **f32), peer_mid_lse=torch.empty(nblk, B, H, **f32),
+                                peer_o=torch.empty(B, H, D, **f32), peer_lse=torch.empty(B, H, **f32))
+    out = torch.empty(B, H, D, dtype=torch.bfloat16, device=dev) if rank == 0 else None
+
+    def step():
+        ringmod.multi_master_decode_attention(q, pool, rt, H, comm, rank, master, peer, fd.flash_decoding_stage1,
+                                              fd.flash_decoding_stage2, out=out)
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize(); dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(); dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    total = int(lens.sum())
+    nparts = sum(int(((max(0, (int(L) - r + P - 1) // P)) + bs - 1) // bs) for L in lens for r in range(P))
+    alg_bytes = float(total) * (2 * H * D * 2) + float(total) * 4 + P * B * H * D * 2 + nparts * H * (D + 1) * 4
+    gbs = alg_bytes / (ms * 1e-3) / 1e9
+    del pool
+    torch.cuda.empty_cache()
+    return {"metric": "distributed_decode_attention_hbm_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "n_gpus": P,
+            "config": {"workload": f"batch {B} x U[4096,65536] tokens ({total} total) split evenly over {P} instances, 1 master, "
+                                   f"{H}x{D} bf16, shuffled token-indexed pools, split {bs}; step = q broadcast + stage 1 + (o,lse) gather + merge"},
+            "roofline": {"bound": "hbm", "achieved": gbs / P, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / P / peaks["hbm"],
+                         "traffic": None, "peak_source": peaks["src"], "per_gpu": True},
+            "algorithmic_bytes": alg_bytes}
+
+
 def cpu_baseline(torch):
     from oracle import esp_oracle as O
     Ts = int(os.environ.get("ESP_BENCH_CPU_TOKENS", "8192"))
@@ -291,15 +375,16 @@ def main():
                                            recv_buffers=recv, attention_fn=ca.context_attention_fwd, init_fn=init_fn,
                                            overlap=not args.no_overlap)
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()                      # nvidia-smi needs a second to start: launch it before the warm-up
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    sampler.mark_start()
     e0.record()
     for _ in range(args.steps):
         step()
@@ -350,6 +435,12 @@ def main():
                "ms_per_step": ems, "steps": n_e2e}
         del hq, hkv, ho
 
+    decode_dist = None
+    if not args.skip_extras and P > 1:
+        del q, kv_local, o, recv
+        torch.cuda.empty_cache()
+        decode_dist = decode_bench_dist(torch, dist, comm, peaks, rank, P)
+
     if rank == 0:
         out = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": P, "steps": args.steps, "warmup": args.warmup,
@@ -369,6 +460,8 @@ def main():
         }
         if e2e is not None:
             out["e2e"] = e2e
+        if decode_dist is not None:
+            out["decode"] = decode_dist
         if not args.skip_extras and P == 1:
             del q, kv_local, o
             torch.cuda.empty_cache()
