@@ -40,6 +40,13 @@ def prefill_flops(T: int) -> float:
     return 4.0 * D * H * T * (T + 1) / 2.0
 
 
+# DRAM traffic per launch of the dominant kernels, from ncu captures (profiles/*.md):
+#  prefill_step_kernel at 262144 tokens on 1 GPU: dram read 20.39 GB + write 2.81 GB (single-pass capture, full size);
+#  decode_stage1_kernel: traffic / algorithmic bytes = 3.9958 / 3.9873 in the batch-8 capture, scaled by the units processed.
+PREFILL_TRAFFIC_262144_1GPU = 23.2e9
+DECODE_TRAFFIC_PER_ALG_BYTE = 3.9958 / 3.9873
+
+
 def load_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -199,7 +206,8 @@ def decode_bench(torch, peaks, steps=10, warmup=3, B=64):
            "config": {"workload": f"batch {B} x U[4096,65536] tokens ({total} total), {H}x{D} bf16, shuffled token-indexed pool, split {bs}",
                       "l2": f"pool ({total * 2 * H * D * 2 / 1e9:.1f} GB) far larger than L2"},
            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
-                        "traffic": None, "peak_source": peaks["src"]},
+                        "traffic": alg_bytes * DECODE_TRAFFIC_PER_ALG_BYTE, "traffic_source": "ncu batch-8 capture scaled by tokens",
+                        "peak_source": peaks["src"]},
            "algorithmic_bytes": alg_bytes, "gpu_launches_per_step": 2}
     del pool
     torch.cuda.empty_cache()
@@ -280,6 +288,39 @@ def decode_bench_dist(torch, dist, comm, peaks, rank, P, steps=10, warmup=3, B=6
             "roofline": {"bound": "hbm", "achieved": gbs / P, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / P / peaks["hbm"],
                          "traffic": None, "peak_source": peaks["src"], "per_gpu": True},
             "algorithmic_bytes": alg_bytes}
+
+
+def scatter_bench(torch, peaks, steps=10, warmup=3, tokens=262144):
+    """Token-granular KV scatter (destindex_copy_kv): `tokens` rows of [2*H, D] bf16 (16 KiB) into shuffled
+    pool slots, int64 slot ids.  HBM-bound; algorithmic bytes = 2 x row bytes + 8 B of index per token."""
+    from loongserve_b200 import kv_ops
+    dev = "cuda"
+    gg = torch.Generator(device=dev).manual_seed(3)
+    src = torch.randn(tokens, 2 * H, D, generator=gg, device=dev, dtype=torch.bfloat16)
+    pool = torch.empty(tokens + 1024, 2 * H, D, dtype=torch.bfloat16, device=dev)
+    dest = torch.randperm(tokens + 1024, device=dev, generator=gg)[:tokens].to(torch.int64)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(warmup):
+        kv_ops.destindex_copy_kv(src, dest, pool)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        kv_ops.destindex_copy_kv(src, dest, pool)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    row = 2 * H * D * 2
+    alg = float(tokens) * (2 * row + 8)
+    gbs = alg / (ms * 1e-3) / 1e9
+    ok = bool(torch.equal(pool[dest[:4096]], src[:4096]))
+    del src, pool
+    torch.cuda.empty_cache()
+    return {"metric": "kv_scatter_hbm_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "bit_exact_sample": ok,
+            "config": {"workload": f"{tokens} token rows x {row} B scattered to shuffled slots (int64 ids)",
+                       "l2": "8 GiB moved per step, far larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
+                         "traffic": None, "peak_source": peaks["src"]},
+            "algorithmic_bytes": alg}
 
 
 def cpu_baseline(torch):
@@ -451,7 +492,9 @@ def main():
                        "l2": "inputs (q 2 GiB + kv 4 GiB per job) far larger than L2, no flush needed",
                        "flop_per_step": flops},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tf_sustained"], "unit": "TFLOP/s",
-                         "frac": per_gpu / peaks["tf_sustained"], "traffic": None, "peak_source": peaks["src"],
+                         "frac": per_gpu / peaks["tf_sustained"],
+                         "traffic": PREFILL_TRAFFIC_262144_1GPU if (P == 1 and T == T_TOTAL) else None,
+                         "peak_source": peaks["src"],
                          "peak_kind": "sustained cuBLAS bf16 (kernel runs for seconds inside the timed loop)",
                          "frac_of_burst_peak": per_gpu / peaks["tf_burst"], "per_gpu": True},
             "clocks": clocks,
@@ -466,6 +509,7 @@ def main():
             del q, kv_local, o
             torch.cuda.empty_cache()
             out["decode"] = decode_bench(torch, peaks)
+            out["scatter"] = scatter_bench(torch, peaks)
             out["cpu_baseline"] = cpu_baseline(torch)
         print(json.dumps(out), flush=True)
     if world > 1:

@@ -185,6 +185,24 @@ __device__ __forceinline__ float chunk_max(uint32_t (&r)[32], int col0, int limi
     return fmaxf(fmax3(a[0], a[1], a[2]), a[3]);
 }
 
+// Packed version of exp2_poly for two values (f32x2 FMA-pipe instructions).
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+    x.x = fmaxf(x.x, -126.f); x.y = fmaxf(x.y, -126.f);
+    const float2 magic = make_float2(12582912.f, 12582912.f);
+    const float2 xf = __fadd2_rd(x, magic);                              // floor(x) in the mantissa
+    const float2 fl = __fadd2_rn(xf, make_float2(-12582912.f, -12582912.f));
+    const float2 f = __ffma2_rn(fl, make_float2(-1.f, -1.f), x);         // x - floor(x) in [0, 1)
+    float2 pz = __ffma2_rn(f, make_float2(0.077119089663028717f, 0.077119089663028717f),
+                           make_float2(0.227564394474029541f, 0.227564394474029541f));
+    pz = __ffma2_rn(pz, f, make_float2(0.695146143436431885f, 0.695146143436431885f));
+    pz = __ffma2_rn(pz, f, make_float2(1.f, 1.f));
+    return make_float2(__uint_as_float(__float_as_uint(pz.x) + (__float_as_uint(xf.x) << 23)),
+                       __uint_as_float(__float_as_uint(pz.y) + (__float_as_uint(xf.y) << 23)));
+}
+
+#ifndef ESP_EXP_VARIANT
+#define ESP_EXP_VARIANT 0
+#endif
 // p = 2^(s*scale - m) for one 32-column chunk; packs to 16-bit pairs and returns the chunk's row sum
 // (two independent packed accumulators)
 template <typename T, int OFF>
@@ -192,18 +210,36 @@ __device__ __forceinline__ float chunk_exp(const uint32_t (&r)[32], float scale,
     const float2 sc2 = make_float2(scale, scale), nm2 = make_float2(neg_m, neg_m);
     float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
     constexpr int kStride = kPolyPer32 > 0 ? 32 / kPolyPer32 : 1;   // every kStride-th pair goes to the FMA pipe
+#if ESP_EXP_VARIANT == 1
+    // staged: all scale/subtract first, then all exponentials, then sums and packing
+    float2 x[16], e[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+        x[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), sc2, nm2);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        if (kPolyPer32 > 0 && (i % kStride) == kStride - 1) e[i] = exp2_poly2(x[i]);
+        else { e[i].x = ex2(x[i].x); e[i].y = ex2(x[i].y); }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        acc[i & 1] = __fadd2_rn(acc[i & 1], e[i]);
+        pk[OFF + i] = Cvt<T>::pack(e[i].x, e[i].y);
+    }
+#else
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
         const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sc2, nm2);
         float2 e;
         if (kPolyPer32 > 0 && ((i / 2) % kStride) == kStride - 1) {
-            e.x = exp2_poly(x.x); e.y = exp2_poly(x.y);
+            e = exp2_poly2(x);
         } else {
             e.x = ex2(x.x); e.y = ex2(x.y);
         }
         acc[(i / 2) & 1] = __fadd2_rn(acc[(i / 2) & 1], e);
         pk[OFF + i / 2] = Cvt<T>::pack(e.x, e.y);
     }
+#endif
     const float2 t = __fadd2_rn(acc[0], acc[1]);
     return t.x + t.y;
 }
