@@ -165,3 +165,117 @@ def test_multi_master_decode_two_gpus(tmp_path):
         rt[b, :L] = torch.arange(off, off + L, dtype=torch.int32); off += L
     ro, rl = O.token_decode_attention(q, kall, vall, rt, torch.arange(B, dtype=torch.int32), torch.tensor(lens, dtype=torch.int32))
     assert torch.allclose(o.float(), ro, atol=2e-2, rtol=1e-2) and torch.allclose(lse, rl, atol=1e-3, rtol=1e-3)
+
+
+def _runtime_worker(rank, world, port, out):
+    dist, comm = _setup(rank, world, port)
+    from loongserve_b200.attention_runtime import ESPAttentionRuntime
+    dev = torch.device("cuda", rank)
+    L, Hq, Hkv, D = 2, 8, 4, 128
+    rt = ESPAttentionRuntime(layers_num=L, q_head_num=Hq, kv_head_num=Hkv, head_dim=D, max_total_token_num=4096, max_req_num=8,
+                             max_seq_length=4096, sp_world_size=world, total_rank=rank, sp_comm=comm, dtype=torch.bfloat16,
+                             device=dev)
+    g = torch.Generator().manual_seed(33)
+    lens = [1500, 64, 777]
+    B, T = len(lens), sum(lens)
+    q = [torch.randn(T, Hq, D, generator=g).to(torch.bfloat16) for _ in range(L)]
+    kv = [torch.randn(T, 2 * Hkv, D, generator=g).to(torch.bfloat16) for _ in range(L)]
+    qd = [torch.randn(B, Hq, D, generator=g).to(torch.bfloat16) for _ in range(L)]       # decode queries
+    local_len = [max(0, (n - rank + world - 1) // world) for n in lens]
+    b_len = torch.tensor(local_len, dtype=torch.int32, device=dev)
+    b_start = torch.cumsum(b_len, 0, dtype=torch.int32) - b_len
+    b_req = torch.arange(B, dtype=torch.int32, device=dev)
+    # scale-down plan: instance 0 keeps the first 60 % of every request, instance 1 the rest
+    cb = torch.tensor([0 if rank == 0 else (6 * n) // 10 for n in lens], dtype=torch.int32, device=dev)
+    ce = torch.tensor([(6 * n) // 10 if rank == 0 else n for n in lens], dtype=torch.int32, device=dev)
+    max_tok = max(sum(max(0, (n - r + world - 1) // world) for n in lens) for r in range(world))
+    st = rt.prepare_prefill(B, sum(local_len), max_tok, max(local_len), b_req, b_start, b_len,
+                            torch.full((B,), rank, dtype=torch.int32, device=dev), list(range(world)), rank,
+                            need_context_migration=True, kv_cache_index_begin=cb, kv_cache_index_end=ce,
+                            request_lengths=lens, striped=True)
+    outs = []
+    for layer in range(L):
+        mine = O.shard_tokens(kv[layer], lens, world, True)[rank]
+        rt.pre_cache_kv(st, layer)[:mine.shape[0]].copy_(mine.to(dev))
+        o = rt.context_attention(O.shard_tokens(q[layer], lens, world, True)[rank].to(dev), st, layer)
+        outs.append(o.cpu())
+    kept = [int(ce[b] - cb[b]) for b in range(B)]
+    # ---- multi-master decode over the kept tokens (instance 0 is the master; no new token is added here)
+    k_len = torch.tensor(kept, dtype=torch.int32, device=dev)
+    f32 = dict(dtype=torch.float32, device=dev)
+    from loongserve_b200 import ring
+    bs = 256
+    nblk = (max(kept) + bs - 1) // bs
+    master = peer = None
+    if rank == 0:
+        master = ring.MasterPlan(peers=list(range(world)), b_req_idx=b_req, b_seq_len=k_len, max_len_in_batch=max(kept), block_seq=bs,
+                                 global_mid_o=torch.empty(world - 1 + nblk, B, Hq, D, **f32), global_mid_lse=torch.empty(world - 1 + nblk, B, Hq, **f32),
+                                 global_merge_len=(world - 1 + (k_len + bs - 1) // bs).to(torch.int32), global_out_lse=torch.empty(B, Hq, **f32))
+    else:
+        peer = ring.PeerPlan(masters=[0], ranges=[(0, B)], peer_query_buffer=torch.empty(B, Hq, D, dtype=torch.bfloat16, device=dev),
+                             peer_b_req_idx=b_req, peer_b_seq_len=k_len, peer_max_len_in_batch=max(kept), block_seq=bs,
+                             peer_mid_o=torch.empty(nblk, B, Hq, D, **f32), peer_mid_lse=torch.empty(nblk, B, Hq, **f32),
+                             peer_o=torch.empty(B, Hq, D, **f32), peer_lse=torch.empty(B, Hq, **f32))
+    dstate = LongServeState(master_plan=master, peer_plan=peer)
+    dec1 = [rt.token_attention(qd[layer].to(dev) if rank == 0 else None, dstate, layer) for layer in range(L)]
+    # ---- decode-stage migration: instance 1 hands the last 100 / 0 / 50 kept tokens of each request to instance 0
+    mig = torch.tensor([100, 0, 50], dtype=torch.int32, device=dev)
+    torch.cuda.synchronize(); dist.barrier()
+    if rank == 0:
+        rt.decoding_stage_migration(True, b_req, mig, k_len, 1, migration_len_sum=150, max_migration_len=100)
+        new_len = k_len + mig
+    else:
+        rt.decoding_stage_migration(False, b_req, mig, k_len, 0, migration_len_sum=150, max_migration_len=100)
+        new_len = k_len - mig
+    if rank == 0:
+        master.b_seq_len = new_len; master.max_len_in_batch = int(new_len.max())
+        nb2 = (int(new_len.max()) + bs - 1) // bs
+        master.global_mid_o = torch.empty(world - 1 + nb2, B, Hq, D, **f32); master.global_mid_lse = torch.empty(world - 1 + nb2, B, Hq, **f32)
+        master.global_merge_len = (world - 1 + (new_len + bs - 1) // bs).to(torch.int32)
+    else:
+        peer.peer_b_seq_len = new_len
+    dec2 = [rt.token_attention(qd[layer].to(dev) if rank == 0 else None, dstate, layer) for layer in range(L)]
+    torch.cuda.synchronize()
+    torch.save(dict(outs=outs, dec1=[x.cpu() if x is not None else None for x in dec1],
+                    dec2=[x.cpu() if x is not None else None for x in dec2], free=rt.mem_manager.can_use_mem_size,
+                    state_sum=int(rt.mem_manager.mem_state.sum()), kept=kept), os.path.join(out, f"rt{rank}.pt"))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+
+
+class LongServeState:
+    def __init__(self, master_plan, peer_plan):
+        self.master_plan, self.peer_plan = master_plan, peer_plan
+
+
+def test_runtime_prefill_keep_decode_migrate_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    mp.spawn(_runtime_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    g = torch.Generator().manual_seed(33)
+    L, Hq, Hkv, D = 2, 8, 4, 128
+    lens = [1500, 64, 777]
+    B, T = len(lens), sum(lens)
+    q = [torch.randn(T, Hq, D, generator=g).to(torch.bfloat16) for _ in range(L)]
+    kv = [torch.randn(T, 2 * Hkv, D, generator=g).to(torch.bfloat16) for _ in range(L)]
+    qd = [torch.randn(B, Hq, D, generator=g).to(torch.bfloat16) for _ in range(L)]
+    parts = [torch.load(os.path.join(str(tmp_path), f"rt{r}.pt")) for r in range(world)]
+    rtab = torch.full((B, max(lens)), O.INT32_MAX, dtype=torch.int32); off = 0
+    for b, n in enumerate(lens):
+        rtab[b, :n] = torch.arange(off, off + n, dtype=torch.int32); off += n
+    for layer in range(L):
+        ro, _ = O.full_causal_attention(q[layer], kv[layer][:, :Hkv], kv[layer][:, Hkv:], lens)
+        o = O.unshard_tokens([p["outs"][layer] for p in parts], lens, world, True)
+        assert bool(((o.float() - ro).abs() <= 2e-2 + 1e-2 * ro.abs()).all())
+        # decode over ALL tokens of every request (the two instances together hold each token exactly once),
+        # identical before and after the migration
+        rd, _ = O.token_decode_attention(qd[layer], kv[layer][:, :Hkv], kv[layer][:, Hkv:], rtab, torch.arange(B, dtype=torch.int32),
+                                         torch.tensor(lens, dtype=torch.int32))
+        for key in ("dec1", "dec2"):
+            got = parts[0][key][layer].float()
+            assert bool(((got - rd).abs() <= 2e-2 + 1e-2 * rd.abs()).all()), key
+    # slot accounting: kept tokens, then 150 tokens moved from instance 1 to instance 0
+    assert parts[0]["free"] == 4096 - sum(parts[0]["kept"]) - 150 and parts[1]["free"] == 4096 - sum(parts[1]["kept"]) + 150
+    assert parts[0]["state_sum"] == sum(parts[0]["kept"]) + 150 and parts[1]["state_sum"] == sum(parts[1]["kept"]) - 150
