@@ -200,6 +200,29 @@ int esp_mig_scatter(const void* recv_buf, int64_t total_tokens, int32_t* req_to_
                     int32_t elem_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Element-wise layer kernels around the attention path (needed only to run a whole Llama layer).
+ */
+
+/* out[t,:] = in[t,:] * rsqrt(mean(in[t,:]^2) + eps) * weight.  Replaces longserve_cuda_kernels.rms_norm
+ *   (longserve_cuda_kernels/src/entrypoints.cpp:15-38, rms_norm.cu:10-60).  Contiguous [tokens, hidden],
+ * hidden a multiple of 8; dtype F16/BF16; fp32 accumulation. */
+int esp_rms_norm(void* out, const void* in, const void* weight, int64_t tokens, int32_t hidden,
+                 float eps, int32_t dtype, void* stream);
+
+/* In-place rotate-half RoPE on x [tokens, heads, head_dim] (strides in elements, last dim contiguous):
+ * x1' = x1*cos - x2*sin, x2' = x1*sin + x2*cos with x1/x2 the first/second half of head_dim;
+ * cos, sin [tokens, head_dim/2] contiguous in x's dtype.  Replaces one half of
+ * longserve_cuda_kernels.rotary_emb (entrypoints.cpp:53-87, rotary_emb.cu:10-51), which rotates q and k
+ * by two such calls.  Math in fp32, rounded once (the reference rounds after every half-precision op). */
+int esp_rotary_emb(void* x, const void* cosv, const void* sinv, int64_t x_stride_t, int64_t x_stride_h,
+                   int64_t tokens, int32_t heads, int32_t head_dim, int32_t dtype, void* stream);
+
+/* io[:, :F] = silu(io[:, :F]) * io[:, F:2F] on a contiguous [tokens, 2F] buffer.  Replaces
+ * longserve_cuda_kernels.silu_and_mul_inplace (entrypoints.cpp:40-51, silu_and_mul.cu:17-45). */
+int esp_silu_and_mul_inplace(void* io, int64_t tokens, int32_t ffn_inter_dim, int32_t dtype,
+                             void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Building-block self check (used by the test-suite): D[128,128] fp32 = A[128,128] * B^T through one
  * tcgen05.mma chain, in the three operand forms the prefill kernel uses.
  * mode 0: A and B K-major in shared memory (the Q*K^T form);

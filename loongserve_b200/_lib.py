@@ -40,6 +40,9 @@ ATTN_SIGNATURES = {
                        _i32, _i32, _i32, _vp],
     "esp_mig_scatter": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32,
                         _i32, _i32, _i32, _i32, _vp],
+    "esp_rms_norm": [_vp, _vp, _vp, _i64, _i32, _f32, _i32, _vp],
+    "esp_rotary_emb": [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _vp],
+    "esp_silu_and_mul_inplace": [_vp, _i64, _i32, _i32, _vp],
     "esp_selftest_umma": [_vp, _vp, _vp, _i32, _i32, _vp],
 }
 ATTN_STRING_FUNCS = {"esp_strerror": [_i32], "esp_last_cuda_error": []}

@@ -1,0 +1,122 @@
+"""A Llama-architecture layer stack around the ESP attention runtime: what the reference's pre / transformer /
+post layer-infer classes do for one SP instance with tp = 1
+(loongserve/models/llama/layer_infer/longserve_transformer_layer_infer.py:70-96, 372-456;
+longserve_pre_layer_infer.py:35-43; longserve_post_layer_infer.py:37-83), with random-initialised weights in the
+reference's fused layouts (layer_weights/longserve_transformer_layer_weight.py:60-117):
+``q_weight_ [hidden, Hq*D]``, ``kv_weight_ [hidden, 2*Hkv*D]``, ``o_weight_ [Hq*D, hidden]``,
+``gate_up_proj [hidden, 2*F]``, ``down_proj [F, hidden]``.
+
+Projections are cuBLAS (``torch.mm``), exactly as in the reference; everything else runs in this package's kernels.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from . import layer_ops
+from .attention_runtime import ESPAttentionRuntime
+
+
+@dataclass
+class LlamaConfig:
+    num_layers: int = 32
+    hidden: int = 4096
+    num_q_heads: int = 32
+    num_kv_heads: int = 32
+    head_dim: int = 128
+    ffn: int = 11008
+    vocab: int = 32000
+    rms_eps: float = 1e-5
+    rope_base: float = 10000.0
+
+
+class LlamaWeights:
+    """Seeded random weights (normal, std 0.02; norm weights 1 + small noise)."""
+
+    def __init__(self, cfg: LlamaConfig, dtype=torch.bfloat16, device="cuda", seed: int = 0):
+        g = torch.Generator(device=device).manual_seed(seed)
+
+        def w(*shape):
+            return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * 0.02).to(dtype)
+
+        def nw(n):
+            return (1.0 + 0.1 * torch.randn(n, generator=g, device=device, dtype=torch.float32)).to(dtype)
+
+        H, Hq, Hkv, D, F = cfg.hidden, cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim, cfg.ffn
+        self.embed = w(cfg.vocab, H)
+        self.layers = []
+        for _ in range(cfg.num_layers):
+            self.layers.append(dict(att_norm=nw(H), q=w(H, Hq * D), kv=w(H, 2 * Hkv * D), o=w(Hq * D, H), ffn_norm=nw(H),
+                                    gate_up=w(H, 2 * F), down=w(F, H)))
+        self.final_norm = nw(H)
+        self.lm_head = w(H, cfg.vocab)
+
+
+def rope_cos_sin(positions: torch.Tensor, head_dim: int, base: float, dtype):
+    """cos/sin rows for the given global positions (rotate-half convention), built in fp32 then cast, as the
+    reference's table is (longserve_model.py:264-275)."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, device=positions.device, dtype=torch.float32) / head_dim))
+    ang = torch.outer(positions.to(torch.float32), inv_freq)
+    return torch.cos(ang).to(dtype).contiguous(), torch.sin(ang).to(dtype).contiguous()
+
+
+class LlamaESPStack:
+    def __init__(self, cfg: LlamaConfig, weights: LlamaWeights, runtime: ESPAttentionRuntime):
+        self.cfg, self.w, self.rt = cfg, weights, runtime
+
+    # ------------------------------------------------------------------ prefill (every instance of the ring)
+    @torch.inference_mode()
+    def prefill(self, input_ids: torch.Tensor, positions: torch.Tensor, st, last_token_rows: Optional[torch.Tensor] = None):
+        """input_ids / positions: this instance's local tokens (packed, request-major) and their global positions;
+        ``st`` from ``ESPAttentionRuntime.prepare_prefill``.  Returns logits of ``last_token_rows`` (local row
+        indices; default: none -> hidden states are returned instead)."""
+        cfg, rt = self.cfg, self.rt
+        Hq, Hkv, D = cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim
+        x = self.w.embed[input_ids.long()]
+        n = x.shape[0]
+        cos, sin = rope_cos_sin(positions, D, cfg.rope_base, x.dtype)
+        for li, lw in enumerate(self.w.layers):
+            h = layer_ops.rms_norm(x, lw["att_norm"], cfg.rms_eps)
+            q = torch.mm(h, lw["q"])
+            cache_kv = rt.pre_cache_kv(st, li)
+            torch.mm(h, lw["kv"], out=cache_kv.view(-1, 2 * Hkv * D)[:n])
+            layer_ops.rotary_emb(q.view(-1, Hq, D), cache_kv[:n, :Hkv, :], cos, sin)
+            o = rt.context_attention(q.view(-1, Hq, D), st, li, out=h.view(-1, Hq, D) if Hq * D == cfg.hidden else None)
+            x.add_(torch.mm(o.view(n, Hq * D), lw["o"]))
+            x.add_(layer_ops.ffn_block(x, lw["ffn_norm"], cfg.rms_eps, lw["gate_up"], lw["down"]))
+        if last_token_rows is None:
+            return x
+        return self._logits(x[last_token_rows.long()])
+
+    # ------------------------------------------------------------------ decode
+    @torch.inference_mode()
+    def decode(self, input_ids: Optional[torch.Tensor], positions: Optional[torch.Tensor], st):
+        """One decode step.  Masters pass their requests' new token ids and global positions and get logits;
+        pure peers pass None and only serve attention for the other masters' queries."""
+        cfg, rt = self.cfg, self.rt
+        Hq, Hkv, D = cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim
+        is_master = st.master_plan is not None
+        if is_master:
+            x = self.w.embed[input_ids.long()]
+            n = x.shape[0]
+            cos, sin = rope_cos_sin(positions, D, cfg.rope_base, x.dtype)
+        for li, lw in enumerate(self.w.layers):
+            if is_master:
+                h = layer_ops.rms_norm(x, lw["att_norm"], cfg.rms_eps)
+                q = torch.mm(h, lw["q"])
+                cache_kv = rt.decode_cache_kv(st, li)
+                torch.mm(h, lw["kv"], out=cache_kv.view(-1, 2 * Hkv * D)[:n])
+                layer_ops.rotary_emb(q.view(-1, Hq, D), cache_kv[:n, :Hkv, :], cos, sin)
+                rt.post_decode_cache_kv(st, li)
+                o = rt.token_attention(q.view(-1, Hq, D), st, li)
+                x.add_(torch.mm(o.view(n, Hq * D), lw["o"]))
+                x.add_(layer_ops.ffn_block(x, lw["ffn_norm"], cfg.rms_eps, lw["gate_up"], lw["down"]))
+            else:
+                rt.token_attention(None, st, li)
+        return self._logits(x) if is_master else None
+
+    def _logits(self, x):
+        h = layer_ops.rms_norm(x.contiguous(), self.w.final_norm, self.cfg.rms_eps)
+        return torch.mm(h, self.w.lm_head).float()

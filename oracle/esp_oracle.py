@@ -456,3 +456,70 @@ class OracleMemoryManager:
     def free_all(self):
         self.mem_state[:] = 0
         self.can_use_mem_size = self.size
+
+
+# ----------------------------------------------------------------------------------------------
+# Layer glue around the attention path (element-wise ops, RoPE tables, one Llama layer)
+# ----------------------------------------------------------------------------------------------
+
+def rms_norm(x, weight, eps):
+    """x * rsqrt(mean(x^2) + eps) * weight, fp32 (longserve_cuda_kernels/test/rms_norm.py:5-7,
+    kernel longserve_cuda_kernels/src/rms_norm.cu:10-46)."""
+    x = x.float()
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+
+
+def rotary_emb(x, cos, sin):
+    """Rotate-half RoPE: first half / second half of head_dim (longserve_cuda_kernels/test/rotary_emb.py:5-14,
+    kernel rotary_emb.cu:26-33)."""
+    x = x.float()
+    T, h, dim = x.shape
+    x0, x1 = x[:, :, : dim // 2], x[:, :, dim // 2:]
+    c = cos.float().view(T, 1, dim // 2); s = sin.float().view(T, 1, dim // 2)
+    return torch.cat((x0 * c - x1 * s, x0 * s + x1 * c), dim=-1)
+
+
+def silu_and_mul(io):
+    """silu(io[:, :F]) * io[:, F:]  (longserve_cuda_kernels/test/silu_and_mul.py, kernel silu_and_mul.cu:17-34)."""
+    io = io.float()
+    F = io.shape[1] // 2
+    return torch.nn.functional.silu(io[:, :F]) * io[:, F:]
+
+
+def ffn_block(x, norm_weight, eps, gate_up_proj, down_proj, act_dtype=None):
+    """norm -> mm(gate_up) -> silu*mul -> mm(down) (longserve_cuda_kernels/src/entrypoints.cpp:89-101).
+    ``act_dtype`` rounds the intermediate activations like the 16-bit pipeline does."""
+    r = (lambda t: t.to(act_dtype).float()) if act_dtype is not None else (lambda t: t)
+    h = r(rms_norm(x, norm_weight, eps))
+    gu = r(h @ gate_up_proj.float())
+    a = r(silu_and_mul(gu))
+    return r(a @ down_proj.float())
+
+
+def rope_tables(positions, head_dim, base=10000.0):
+    """cos/sin [len(positions), head_dim/2] of the rotate-half convention, fp32:
+    angle = position * base^(-2i/head_dim) (loongserve/models/llama/longserve_model.py:264-275)."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    ang = torch.outer(positions.float(), inv_freq)
+    return torch.cos(ang), torch.sin(ang)
+
+
+def llama_layer(x, positions, lens, w, eps, Hq, Hkv, D, act_dtype=None):
+    """One full-sequence Llama layer on packed sequences (prefill), fp32 math with optional 16-bit rounding of
+    the activations: att_norm -> q / kv projections -> RoPE on q and k -> causal attention -> o projection ->
+    residual -> ffn_block -> residual (longserve_transformer_layer_infer.py:70-96, 372-407).
+    ``w`` holds att_norm, q, kv, o, ffn_norm, gate_up, down.  Returns (x_out, k, v)."""
+    r = (lambda t: t.to(act_dtype).float()) if act_dtype is not None else (lambda t: t)
+    x = x.float()
+    h = r(rms_norm(x, w["att_norm"], eps))
+    q = r(h @ w["q"].float()).view(-1, Hq, D)
+    kv = r(h @ w["kv"].float()).view(-1, 2 * Hkv, D)
+    cos, sin = rope_tables(positions, D)
+    cos, sin = r(cos), r(sin)
+    q = r(rotary_emb(q, cos, sin))
+    k = r(rotary_emb(kv[:, :Hkv], cos, sin))
+    v = kv[:, Hkv:]
+    o, _ = full_causal_attention(q, k, v, lens)
+    x = r(x + r(r(o).reshape(-1, Hq * D) @ w["o"].float()))
+    x = r(x + ffn_block(x, w["ffn_norm"], eps, w["gate_up"], w["down"], act_dtype))
+    return x, k, v

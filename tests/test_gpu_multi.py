@@ -279,3 +279,71 @@ def test_runtime_prefill_keep_decode_migrate_two_gpus(tmp_path):
     # slot accounting: kept tokens, then 150 tokens moved from instance 1 to instance 0
     assert parts[0]["free"] == 4096 - sum(parts[0]["kept"]) - 150 and parts[1]["free"] == 4096 - sum(parts[1]["kept"]) + 150
     assert parts[0]["state_sum"] == sum(parts[0]["kept"]) + 150 and parts[1]["state_sum"] == sum(parts[1]["kept"]) - 150
+
+
+def _two_masters_worker(rank, world, port, out):
+    """Both instances are masters of their own mini-batch and peers for the other's
+    (the multi-master case: pre_process.py:194-230, longserve_transformer_layer_infer.py:247-265)."""
+    dist, comm = _setup(rank, world, port)
+    from loongserve_b200.attention_runtime import ESPAttentionRuntime
+    dev = torch.device("cuda", rank)
+    Hq, Hkv, D = 8, 2, 128
+    rt = ESPAttentionRuntime(layers_num=1, q_head_num=Hq, kv_head_num=Hkv, head_dim=D, max_total_token_num=8192, max_req_num=16,
+                             max_seq_length=4096, sp_world_size=world, total_rank=rank, sp_comm=comm, dtype=torch.float16, device=dev)
+    g = torch.Generator().manual_seed(77)
+    # requests 0..2 belong to master 0, requests 3..4 to master 1; lengths include the new token
+    lens = [900, 33, 2000, 513, 1500]
+    owner = [0, 0, 0, 1, 1]
+    kv = [torch.randn(n, 2 * Hkv, D, generator=g).to(torch.float16) for n in lens]
+    q = torch.randn(len(lens), Hq, D, generator=g).to(torch.float16)
+    # existing tokens (all but the new one) are spread round-robin over the two instances; the new token's KV goes to its master
+    slot = 0
+    local_cnt = []
+    for b, n in enumerate(lens):
+        mine = [t for t in range(n - 1) if t % world == rank]
+        rows = torch.tensor(mine, dtype=torch.long)
+        rt.mem_manager.kv_buffer[0][slot:slot + len(mine)] = kv[b][rows].to(dev)
+        rt.req_manager.req_to_token_indexs[b, :len(mine)] = torch.arange(slot, slot + len(mine), dtype=torch.int32, device=dev)
+        slot += len(mine); local_cnt.append(len(mine))
+    rt.mem_manager.add_refs(torch.arange(slot, device=dev))
+    my_reqs = [b for b in range(len(lens)) if owner[b] == rank]
+    other_reqs = [b for b in range(len(lens)) if owner[b] != rank]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    my_len = [local_cnt[b] + 1 for b in my_reqs]                      # + the new token
+    st = rt.prepare_decode(len(my_reqs), len(my_reqs), max(my_len), i32(my_reqs), i32(my_len), i32([lens[b] - 1 for b in my_reqs]),
+                           rank, list(range(world)), rank, peer_sp_master_rank_list=[1 - rank],
+                           peer_query_buffer_range_list=[(0, len(other_reqs))], peer_batch_size=len(other_reqs),
+                           peer_max_len_in_batch=max(local_cnt[b] for b in other_reqs), peer_b_req_idx=i32(other_reqs),
+                           peer_b_seq_len=i32([local_cnt[b] for b in other_reqs]))
+    new_rows = torch.stack([kv[b][lens[b] - 1] for b in my_reqs]).to(dev)
+    rt.decode_cache_kv(st, 0).copy_(new_rows)
+    rt.post_decode_cache_kv(st, 0)
+    o = rt.token_attention(q[my_reqs].to(dev), st, 0)
+    torch.cuda.synchronize()
+    torch.save(dict(o=o.cpu(), lse=st.global_out_logexpsum.cpu(), reqs=my_reqs), os.path.join(out, f"mm{rank}.pt"))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+
+
+def test_two_masters_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    mp.spawn(_two_masters_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    g = torch.Generator().manual_seed(77)
+    Hq, Hkv, D = 8, 2, 128
+    lens = [900, 33, 2000, 513, 1500]
+    kv = [torch.randn(n, 2 * Hkv, D, generator=g).to(torch.float16) for n in lens]
+    q = torch.randn(len(lens), Hq, D, generator=g).to(torch.float16)
+    allkv = torch.cat(kv, 0)
+    rtab = torch.full((len(lens), max(lens)), O.INT32_MAX, dtype=torch.int32); off = 0
+    for b, n in enumerate(lens):
+        rtab[b, :n] = torch.arange(off, off + n, dtype=torch.int32); off += n
+    ro, rl = O.token_decode_attention(q, allkv[:, :Hkv], allkv[:, Hkv:], rtab, torch.arange(len(lens), dtype=torch.int32),
+                                      torch.tensor(lens, dtype=torch.int32))
+    for r in range(world):
+        p = torch.load(os.path.join(str(tmp_path), f"mm{r}.pt"))
+        got, want = p["o"].float(), ro[p["reqs"]]
+        assert bool(((got - want).abs() <= 2e-2 + 1e-2 * want.abs()).all())
+        assert torch.allclose(p["lse"], rl[p["reqs"]], atol=1e-3, rtol=1e-3)
