@@ -323,6 +323,108 @@ def scatter_bench(torch, peaks, steps=10, warmup=3, tokens=262144):
             "algorithmic_bytes": alg}
 
 
+def e2e_llama(args):
+    """End-to-end Llama-2-7B-architecture run (the fifth benchmark configuration when launched on 8 GPUs): one
+    prefill of `--e2e-tokens` uniform-random token ids striped over the N instances, then `--e2e-decode-steps`
+    decode steps with the KV distributed over all instances (instance 0 is the master and keeps the new tokens).
+    Random-init bf16 weights, seeded; projections are cuBLAS, everything else this package's kernels."""
+    import torch
+    import torch.distributed as dist
+    from loongserve_b200.attention_runtime import ESPAttentionRuntime
+    from loongserve_b200.llama_stack import LlamaConfig, LlamaESPStack, LlamaWeights
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    comm = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        from loongserve_b200 import rnccl
+        idt = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            idt = torch.tensor(rnccl.get_nccl_unique_id(), dtype=torch.uint8, device=dev)
+        dist.broadcast(idt, 0)
+        comm = rnccl.RNCCLComm(idt.cpu().tolist(), world, rank)
+    P, T, steps = world, args.e2e_tokens, args.e2e_decode_steps
+    cfg = LlamaConfig(num_layers=args.e2e_layers)
+    Tl = (T - rank + P - 1) // P
+    max_tok = (T + P - 1) // P
+    rt = ESPAttentionRuntime(layers_num=cfg.num_layers, q_head_num=cfg.num_q_heads, kv_head_num=cfg.num_kv_heads,
+                             head_dim=cfg.head_dim, max_total_token_num=max_tok + steps + 64, max_req_num=4,
+                             max_seq_length=max_tok + steps + 64, sp_world_size=P, total_rank=rank, sp_comm=comm,
+                             dtype=torch.bfloat16, device=dev, decode_block_seq=1024)
+    stack = LlamaESPStack(cfg, LlamaWeights(cfg, torch.bfloat16, dev, seed=0), rt)
+    g = torch.Generator(device=dev).manual_seed(7)
+    ids_all = torch.randint(0, cfg.vocab, (T,), generator=g, device=dev)        # same stream on every rank
+    ids = ids_all[rank::P].contiguous()
+    pos = torch.arange(rank, T, P, device=dev)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    b_req = i32([0])
+    # untimed warm-up on a throw-away request: NCCL connections, cuBLAS workspaces, kernel attributes
+    wl = 512
+    wst = rt.prepare_prefill(1, wl, wl, wl, i32([1]), i32([0]), i32([wl]), i32([rank]), list(range(P)), rank,
+                             request_lengths=[wl * P], striped=True)
+    stack.prefill(ids[:wl], pos[:wl], wst)
+    if rank == 0:
+        wd = rt.prepare_decode(1, 1, wl + 1, i32([1]), i32([wl + 1]), i32([wl * P]), 0, list(range(P)), 0)
+        stack.decode(i32([1]), i32([wl * P]), wd)
+    else:
+        wd = rt.prepare_decode(0, 0, 0, None, None, None, None, list(range(P)), rank, peer_sp_master_rank_list=[0],
+                               peer_query_buffer_range_list=[(0, 1)], peer_batch_size=1, peer_max_len_in_batch=wl,
+                               peer_b_req_idx=i32([1]), peer_b_seq_len=i32([wl]))
+        stack.decode(None, None, wd)
+    torch.cuda.synchronize()
+    rt.mem_manager.free_all()
+    del wst, wd
+    if world > 1:
+        dist.barrier()
+    p0, p1, d0, d1 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+    p0.record()
+    st = rt.prepare_prefill(1, Tl, max_tok, Tl, b_req, i32([0]), i32([Tl]), i32([rank]), list(range(P)), rank,
+                            request_lengths=[T], striped=True)
+    last_owner = (T - 1) % P
+    logits = stack.prefill(ids, pos, st, last_token_rows=i32([Tl - 1]) if rank == last_owner else None)
+    p1.record()
+    torch.cuda.synchronize()
+    finite = bool(torch.isfinite(logits).all())
+    if world > 1:
+        dist.barrier()
+    local_cnt = Tl
+    tok = i32([1])
+    d0.record()
+    for s_ in range(steps):
+        if rank == 0:
+            local_cnt += 1
+            dst = rt.prepare_decode(1, 1, local_cnt, b_req, i32([local_cnt]), i32([T + s_]), 0, list(range(P)), 0)
+            lg = stack.decode(tok, i32([T + s_]), dst)
+            tok = torch.argmax(lg, dim=-1).to(torch.int32)
+        else:
+            dst = rt.prepare_decode(0, 0, 0, None, None, None, None, list(range(P)), rank, peer_sp_master_rank_list=[0],
+                                    peer_query_buffer_range_list=[(0, 1)], peer_batch_size=1, peer_max_len_in_batch=local_cnt,
+                                    peer_b_req_idx=b_req, peer_b_seq_len=i32([local_cnt]))
+            stack.decode(None, None, dst)
+    d1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([p0.elapsed_time(p1), d0.elapsed_time(d1) / max(steps, 1), 0.0 if finite else 1.0], device=dev)
+    if world > 1:
+        dist.barrier()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        pre_ms, dec_ms, bad = (float(x) for x in t.tolist())
+        attn_flops = cfg.num_layers * 4.0 * cfg.head_dim * cfg.num_q_heads * T * (T + 1) / 2.0
+        print(json.dumps({
+            "metric": "e2e_llama_prefill_tokens_per_s", "value": T / (pre_ms * 1e-3), "unit": "tokens/s", "n_gpus": P,
+            "prefill_ms": pre_ms, "decode_ms_per_step": dec_ms, "decode_steps": steps, "higher_is_better": True,
+            "dtype": "bf16", "data": "synthetic", "outputs_finite": bad == 0.0,
+            "prefill_attention_tflops_equiv": attn_flops / (pre_ms * 1e-3) / 1e12,
+            "config": {"workload": f"Llama-2-7B architecture ({cfg.num_layers} layers, hidden {cfg.hidden}, {cfg.num_q_heads} heads x {cfg.head_dim}, "
+                                   f"FFN {cfg.ffn}, vocab {cfg.vocab}), random-init bf16 weights; one {T}-token prefill at ESP={P} (striped), "
+                                   f"then {steps} decode steps with the KV distributed over all {P} GPUs"}}), flush=True)
+    if world > 1:
+        comm.close()
+        dist.destroy_process_group()
+
+
 def cpu_baseline(torch):
     from oracle import esp_oracle as O
     Ts = int(os.environ.get("ESP_BENCH_CPU_TOKENS", "8192"))
@@ -356,7 +458,14 @@ def main():
     ap.add_argument("--skip-extras", action="store_true", help="skip e2e / decode / cpu baseline (profiling runs)")
     ap.add_argument("--decode-only", action="store_true", help="run only the decode part (profiling runs)")
     ap.add_argument("--decode-batch", type=int, default=64)
+    ap.add_argument("--e2e", action="store_true", help="run the end-to-end Llama-architecture configuration instead")
+    ap.add_argument("--e2e-tokens", type=int, default=524288)
+    ap.add_argument("--e2e-decode-steps", type=int, default=128)
+    ap.add_argument("--e2e-layers", type=int, default=32)
     args = ap.parse_args()
+    if args.e2e:
+        e2e_llama(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
         return
