@@ -232,6 +232,12 @@ int esp_silu_and_mul_inplace(void* io, int64_t tokens, int32_t ffn_inter_dim, in
 int esp_selftest_umma(const void* a, const void* b, float* d, int32_t mode, int32_t dtype,
                       void* stream);
 
+/* Self check of the bounded-wait pattern every in-kernel wait of this library follows: a one-block kernel
+ * waits on an mbarrier that nothing ever completes, for at most `limit_cycles` SM cycles (<= 4e9), then
+ * writes 1 to *result_dev (device int) and returns normally; the context stays usable.  (2 would mean the
+ * barrier completed, which cannot happen.) */
+int esp_selftest_bounded_wait(int64_t limit_cycles, int32_t* result_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -44,6 +44,7 @@ ATTN_SIGNATURES = {
     "esp_rotary_emb": [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _vp],
     "esp_silu_and_mul_inplace": [_vp, _i64, _i32, _i32, _vp],
     "esp_selftest_umma": [_vp, _vp, _vp, _i32, _i32, _vp],
+    "esp_selftest_bounded_wait": [_i64, _vp, _vp],
 }
 ATTN_STRING_FUNCS = {"esp_strerror": [_i32], "esp_last_cuda_error": []}
 

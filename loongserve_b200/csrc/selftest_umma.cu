@@ -92,9 +92,33 @@ __global__ void __launch_bounds__(128, 1) selftest_umma_kernel(const T* __restri
     if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, 256); }
 }
 
+// One thread waits on an mbarrier that nobody ever arrives at, for at most `limit_cycles`, then records the
+// give-up in `result` (1 = timed out as intended, 2 = barrier unexpectedly completed) and returns normally.
+__global__ void selftest_bounded_wait_kernel(long long limit_cycles, int* result) {
+    __shared__ __align__(8) unsigned long long s_bar;
+    const uint32_t bar = smem_u32(&s_bar);
+    if (threadIdx.x == 0) { mbar_init(bar, 1); fence_barrier_init(); }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const long long t0 = clock64();
+        int r = 1;
+        while (clock64() - t0 < limit_cycles) {
+            if (mbar_try_wait(bar, 0)) { r = 2; break; }
+        }
+        *result = r;
+    }
+}
+
 }  // namespace esp
 
 using namespace esp;
+
+extern "C" int esp_selftest_bounded_wait(int64_t limit_cycles, int32_t* result_dev, void* stream) {
+    if (!result_dev || limit_cycles <= 0 || limit_cycles > 4000000000LL) return ESP_ERR_BAD_ARG;
+    selftest_bounded_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit_cycles, result_dev);
+    ESP_LAUNCH_CHECK("selftest_bounded_wait_kernel");
+    return ESP_OK;
+}
 
 extern "C" int esp_selftest_umma(const void* a, const void* b, float* d, int32_t mode, int32_t dtype, void* stream) {
     if (!a || !b || !d || mode < 0 || mode > 2) return ESP_ERR_BAD_ARG;
