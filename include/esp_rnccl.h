@@ -6,7 +6,9 @@
  *
  * Differences from the reference, on purpose: every call returns a status instead of exiting the
  * process (rnccl/src/main.cpp:9-27); the fences take the stream to fence against instead of assuming
- * the legacy default stream (:231-257), and reuse one event instead of creating one per call.
+ * the legacy default stream (:231-257), and reuse one event instead of creating one per call; the private stream has
+ * the highest priority (the reference uses priority 0, :133) so that exchange kernels are not queued behind the
+ * blocks of a running attention kernel.
  */
 #ifndef ESP_RNCCL_H_
 #define ESP_RNCCL_H_

@@ -50,7 +50,11 @@ extern "C" int esp_rnccl_create(const uint8_t id_bytes[ESP_RNCCL_UNIQUE_ID_BYTES
     if (e != cudaSuccess) { delete c; return fail_cuda(e, "cudaGetDevice"); }
     ncclResult_t r = ncclCommInitRank(&c->comm, world_size, id, rank);
     if (r != ncclSuccess) { delete c; return fail_nccl(r, "ncclCommInitRank"); }
-    e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    // Highest priority: the exchange kernels must get SM slots ahead of the queued blocks of a long attention
+    // kernel that is already running, otherwise a small send waits for the whole kernel.
+    int prio_least = 0, prio_greatest = 0;
+    e = cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest);
+    if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&c->stream, cudaStreamNonBlocking, prio_greatest);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_in, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_out, cudaEventDisableTiming);
     if (e != cudaSuccess) { ncclCommDestroy(c->comm); delete c; return fail_cuda(e, "stream/event creation"); }

@@ -187,6 +187,10 @@ def multi_master_decode_attention(q, pool_layer, req_to_token_indexs, num_kv_hea
         stage2_fn(peer.peer_o, peer.peer_lse, peer.peer_b_seq_len, peer.peer_mid_o, peer.peer_mid_lse, peer.block_seq)
         comm.wait_for_default_stream()
 
+    if master is not None and peer is None:
+        # start the (spinning) receive of the partials only once this instance's own stage 1 is done,
+        # so that it does not hold SM slots while stage 1 runs; the peers finish at about the same time
+        comm.wait_for_default_stream()
     comm.nccl_group_start()
     if master is not None:
         others = [r for r in master.peers if r != my_rank]
