@@ -214,7 +214,7 @@ def decode_bench(torch, peaks, steps=10, warmup=3, B=64):
     return out
 
 
-def decode_bench_dist(torch, dist, comm, peaks, rank, P, steps=10, warmup=3, B=64):
+def decode_bench_dist(torch, dist, comm, peaks, rank, P, steps=10, warmup=3, B=64, fused=False):
     """Distributed flash-decoding over P instances (BASELINE config 3): every request's tokens are split
     evenly over the instances (token t on instance t mod P), instance 0 is the master.  A step is the
     whole exchange: q broadcast -> split-KV stage 1 on every instance -> peers merge and send fp32
@@ -259,10 +259,26 @@ def decode_bench_dist(torch, dist, comm, peaks, rank, P, steps=10, warmup=3, B=6
                                 peer_mid_o=torch.empty(nblk, B, H, D, **f32), peer_mid_lse=torch.empty(nblk, B, H, **f32),
                                 peer_o=torch.empty(B, H, D, **f32), peer_lse=torch.empty(B, H, **f32))
     out = torch.empty(B, H, D, dtype=torch.bfloat16, device=dev) if rank == 0 else None
+    grp = None
+    if fused:
+        # exchange over peer memory (NVLink stores + flags inside the kernels) instead of NCCL messages
+        from loongserve_b200.peer_decode import FusedDecodeGroup
+
+        def gather(b):
+            lst = [None] * P
+            dist.all_gather_object(lst, b)
+            return lst
+
+        grp = FusedDecodeGroup(rank, P, 0, B, H, D, gather)
+        f_mid_o = torch.empty(nblk, B, H, D, **f32); f_mid_l = torch.empty(nblk, B, H, **f32)
+        f_lse = torch.empty(B, H, **f32)
 
     def step():
-        ringmod.multi_master_decode_attention(q, pool, rt, H, comm, rank, master, peer, fd.flash_decoding_stage1,
-                                              fd.flash_decoding_stage2, out=out)
+        if fused:
+            grp.step(q, pool, rt, H, b_req, b_len, mx, bs, f_mid_o, f_mid_l, out=out, out_lse=f_lse)
+        else:
+            ringmod.multi_master_decode_attention(q, pool, rt, H, comm, rank, master, peer, fd.flash_decoding_stage1,
+                                                  fd.flash_decoding_stage2, out=out)
 
     for _ in range(warmup):
         step()
@@ -280,9 +296,15 @@ def decode_bench_dist(torch, dist, comm, peaks, rank, P, steps=10, warmup=3, B=6
     nparts = sum(int(((max(0, (int(L) - r + P - 1) // P)) + bs - 1) // bs) for L in lens for r in range(P))
     alg_bytes = float(total) * (2 * H * D * 2) + float(total) * 4 + P * B * H * D * 2 + nparts * H * (D + 1) * 4
     gbs = alg_bytes / (ms * 1e-3) / 1e9
+    status = None
+    if grp is not None:
+        status = list(grp.device_status())
+        dist.barrier()
+        grp.close()
     del pool
     torch.cuda.empty_cache()
     return {"metric": "distributed_decode_attention_hbm_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "n_gpus": P,
+            "exchange": "peer memory (NVLink stores + flags in the kernels)" if fused else "NCCL send/recv", "device_status": status,
             "config": {"workload": f"batch {B} x U[4096,65536] tokens ({total} total) split evenly over {P} instances, 1 master, "
                                    f"{H}x{D} bf16, shuffled token-indexed pools, split {bs}; step = q broadcast + stage 1 + (o,lse) gather + merge"},
             "roofline": {"bound": "hbm", "achieved": gbs / P, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / P / peaks["hbm"],
@@ -585,11 +607,12 @@ def main():
                "ms_per_step": ems, "steps": n_e2e}
         del hq, hkv, ho
 
-    decode_dist = None
+    decode_dist = decode_fused = None
     if not args.skip_extras and P > 1:
         del q, kv_local, o, recv
         torch.cuda.empty_cache()
         decode_dist = decode_bench_dist(torch, dist, comm, peaks, rank, P)
+        decode_fused = decode_bench_dist(torch, dist, comm, peaks, rank, P, fused=True)
 
     if rank == 0:
         out = {
@@ -614,6 +637,7 @@ def main():
             out["e2e"] = e2e
         if decode_dist is not None:
             out["decode"] = decode_dist
+            out["decode_peer_memory"] = decode_fused
         if not args.skip_extras and P == 1:
             del q, kv_local, o
             torch.cuda.empty_cache()

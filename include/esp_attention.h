@@ -128,6 +128,50 @@ int esp_decode_attention_noalloc(void* o, float* out_lse, const void* q, const v
                                  int32_t dtype, int32_t o_dtype, float sm_scale, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Distributed decode over peer memory (NVLink loads/stores instead of NCCL messages).  The reference moves the
+ * queries and the partial results with grouped ncclSend/ncclRecv (_selective_broadcast / _selective_gather /
+ * _selective_scatter, longserve_transformer_layer_infer.py:468-504, used at :247-265 and :337-353); these
+ * entry points do the same exchange inside the compute kernels: the master pushes q into every peer's
+ * buffer and raises a flag there; a peer's stage 1 waits for that flag, its merge writes the fp32 (o, lse)
+ * partial straight into the master's partial buffer, a one-word signal publishes it, and the master's merge
+ * waits for the peers' flags.  Flags are int32 counters that only grow (one value per step).  Every wait is
+ * bounded (about a second) and reports through esp_decode_device_status.
+ */
+
+/* A zero-filled device buffer that other processes on this node can map (CUDA IPC).  esp_peer_buffer_create
+ * ALLOCATES (cudaMalloc) and returns the 64-byte handle to hand to the peers; esp_peer_buffer_open maps a peer's
+ * buffer into this process.  Set-up time only. */
+int esp_peer_buffer_create(int64_t bytes, void** dev_ptr, uint8_t handle_out[64]);
+int esp_peer_buffer_open(const uint8_t handle[64], void** dev_ptr);
+int esp_peer_buffer_close(void* dev_ptr);
+int esp_peer_buffer_destroy(void* dev_ptr);
+
+/* Copy `bytes` (multiple of 16) from src into each of the n_peers (<= 16) destination buffers (peer-mapped
+ * pointers, host arrays of device pointers), then store flag_value to each peer's flag with release semantics. */
+int esp_peer_push(const void* src, void* const* peer_dst, int32_t* const* peer_flags, int32_t n_peers,
+                  int64_t bytes, int32_t flag_value, void* stream);
+/* Publish everything this stream has written so far to the owner of remote_flag: *remote_flag = value. */
+int esp_peer_signal(int32_t* remote_flag, int32_t value, void* stream);
+
+/* esp_decode_stage1 whose blocks first wait until *wait_flag >= wait_value (q then lives in a buffer the
+ * master pushed into) and read q past the L1 cache. */
+int esp_decode_stage1_gated(float* mid_o, float* mid_lse, const void* q, const void* k, const void* v,
+                            int64_t k_stride_t, int64_t k_stride_h, int64_t v_stride_t,
+                            int64_t v_stride_h, const int32_t* req_to_tokens,
+                            int64_t req_to_tokens_stride, const int32_t* b_req_idx,
+                            const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
+                            int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
+                            int32_t seq_block_size, int32_t dtype, float sm_scale,
+                            const int32_t* wait_flag, int32_t wait_value, void* stream);
+/* esp_decode_merge whose blocks first wait until wait_flags[i] >= wait_value for all i < n_wait. */
+int esp_decode_merge_gated(void* o, float* out_lse, const int32_t* b_seqlen, const float* mid_o,
+                           const float* mid_lse, int32_t batch, int32_t num_heads, int32_t head_dim,
+                           int32_t num_blocks, int32_t block_seq, int32_t o_dtype,
+                           const int32_t* wait_flags, int32_t n_wait, int32_t wait_value, void* stream);
+/* Status of the bounded flag waits on the current device, like esp_device_status. */
+int esp_decode_device_status(int32_t out[4], int32_t clear);
+
+/* ------------------------------------------------------------------------------------------------
  * Token-indexed KV pool: scatter, registration, migration (all bit-exact copies / integer work).
  * Rows are [heads2, D] with D contiguous; `row_stride` = token stride, `head_stride` = head stride.
  * `elem_bytes` is 2 for fp16/bf16.  Index arrays may be int32 or int64 (`idx64` != 0).

@@ -18,6 +18,45 @@ constexpr int kDecUnroll = 4;             // tokens per half-warp per step
 constexpr int kDecChunk = 1024;           // slot ids staged in shared memory per chunk
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
+constexpr long long kGateLimitCycles = 2000000000LL;   // about a second: bound of every cross-GPU flag wait
+
+// Status of the bounded flag waits of the gated (peer-memory) decode kernels: {code, block, which, value}.
+__device__ int g_decode_status[4];
+
+__device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {      // bypass L1: the data was written by another GPU
+    uint4 r;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+// One thread waits until *flag >= value (flags only ever grow).  Gives up after kGateLimitCycles, or at once
+// when an earlier wait on this device already failed; then records the failure and returns false.
+__device__ __noinline__ bool gate_wait(const int32_t* flag, int value, int which) {
+    if (ld_acquire_sys(flag) >= value) return true;
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    while (ld_acquire_sys(flag) < value) {
+        if ((++spins & 255u) == 0) {
+            if (*reinterpret_cast<volatile int*>(&g_decode_status[0]) != 0) return false;
+            if (clock64() - t0 > kGateLimitCycles) {
+                if (atomicCAS(&g_decode_status[0], 0, ESP_ERR_DEVICE_TIMEOUT) == 0) {
+                    g_decode_status[1] = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+                    g_decode_status[2] = which;
+                    g_decode_status[3] = value;
+                }
+                return false;
+            }
+        }
+    }
+    return true;
+}
 
 template <typename T, int G>
 __global__ void __launch_bounds__(kDecThreads) decode_stage1_kernel(
@@ -26,7 +65,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_stage1_kernel(
     int64_t v_stride_t, int64_t v_stride_h, const int32_t* __restrict__ req_to_tokens,
     int64_t rtt_stride, const int32_t* __restrict__ b_req_idx, const int32_t* __restrict__ b_seqlen,
     int batch, int num_q_heads, int group /* q heads per kv head */, int seq_block_size,
-    float scale_log2) {
+    float scale_log2, const int32_t* __restrict__ wait_flag, int wait_value) {
     const int blk = blockIdx.x;
     const int hg = blockIdx.y;            // group of G consecutive q heads
     const int b = blockIdx.z;
@@ -44,11 +83,21 @@ __global__ void __launch_bounds__(kDecThreads) decode_stage1_kernel(
     __shared__ int32_t s_slots[kDecChunk];
     __shared__ float s_red[4][G][128 + 2];
 
+    // Gated form: q is pushed into this GPU's memory by the master; wait (bounded) until it has arrived.
+    const bool gated = wait_flag != nullptr;
+    if (gated) {
+        __shared__ int s_go;
+        if (threadIdx.x == 0) s_go = gate_wait(wait_flag, wait_value, 1) ? 1 : 0;
+        __syncthreads();
+        if (!s_go) return;
+    }
+
     // q (pre-scaled into the log2 domain), 8 dims per lane
     float qf[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        const uint4 qv = *reinterpret_cast<const uint4*>(q + ((int64_t)b * num_q_heads + h0 + g) * 128 + hl * 8);
+        const T* qp = q + ((int64_t)b * num_q_heads + h0 + g) * 128 + hl * 8;
+        const uint4 qv = gated ? ld_cg_v4(qp) : *reinterpret_cast<const uint4*>(qp);
         const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -193,7 +242,19 @@ template <typename OT>
 __global__ void __launch_bounds__(128) decode_merge_kernel(
     OT* __restrict__ o, float* __restrict__ out_lse, const int32_t* __restrict__ b_seqlen,
     const float* __restrict__ mid_o, const float* __restrict__ mid_lse, int batch, int num_heads,
-    int num_blocks, int block_seq) {
+    int num_blocks, int block_seq, const int32_t* __restrict__ wait_flags, int n_wait, int wait_value) {
+    // Gated form: the first n_wait partials are written into this GPU's memory by the peers; each peer raises
+    // its flag when its partial is complete.
+    if (wait_flags != nullptr) {
+        __shared__ int s_go;
+        if (threadIdx.x == 0) {
+            int okf = 1;
+            for (int i = 0; i < n_wait && okf; ++i) okf = gate_wait(wait_flags + i, wait_value, 2) ? 1 : 0;
+            s_go = okf;
+        }
+        __syncthreads();
+        if (!s_go) return;
+    }
     const int lane = threadIdx.x & 31;
     const int64_t pair = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (pair >= (int64_t)batch * num_heads) return;
@@ -203,7 +264,7 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(
     if (n > num_blocks) n = num_blocks;
     const int64_t bh = (int64_t)batch * num_heads;
     float M = -INFINITY;
-    for (int j = lane; j < n; j += 32) M = fmaxf(M, mid_lse[j * bh + pair]);
+    for (int j = lane; j < n; j += 32) M = fmaxf(M, __ldcg(mid_lse + j * bh + pair));
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -211,14 +272,14 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(
     if (M > -INFINITY) {
         for (int j0 = 0; j0 < n; j0 += 32) {
             const int j = j0 + lane;
-            const float wl = j < n ? __expf(mid_lse[j * bh + pair] - M) : 0.f;
+            const float wl = j < n ? __expf(__ldcg(mid_lse + j * bh + pair) - M) : 0.f;
             wsum += wl;
             const int cnt = min(32, n - j0);
 #pragma unroll 4
             for (int jj = 0; jj < cnt; ++jj) {
                 const float w = __shfl_sync(0xffffffffu, wl, jj);
                 if (w > 0.f) {
-                    const float4 x = *reinterpret_cast<const float4*>(mid_o + ((j0 + jj) * bh + pair) * 128 + lane * 4);
+                    const float4 x = __ldcg(reinterpret_cast<const float4*>(mid_o + ((j0 + jj) * bh + pair) * 128 + lane * 4));
                     acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y);
                     acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
                 }
@@ -238,7 +299,7 @@ static int launch_stage1(float* mid_o, float* mid_lse, const void* q, const void
                          int64_t kst, int64_t ksh, int64_t vst, int64_t vsh, const int32_t* rtt,
                          int64_t rtt_stride, const int32_t* b_req_idx, const int32_t* b_seqlen,
                          int batch, int Hq, int Hkv, int max_len, int bs, float scale_log2,
-                         cudaStream_t s) {
+                         cudaStream_t s, const int32_t* wait_flag = nullptr, int wait_value = 0) {
     const int group = Hq / Hkv;
     const int nblk = (max_len + bs - 1) / bs;
     int G = 1;
@@ -246,7 +307,7 @@ static int launch_stage1(float* mid_o, float* mid_lse, const void* q, const void
     dim3 grid(nblk, Hq / G, batch);
 #define ESP_S1(GG) decode_stage1_kernel<T, GG><<<grid, kDecThreads, 0, s>>>(mid_o, mid_lse, (const T*)q, \
         (const T*)k, (const T*)v, kst, ksh, vst, vsh, rtt, rtt_stride, b_req_idx, b_seqlen, batch, Hq, \
-        group, bs, scale_log2)
+        group, bs, scale_log2, wait_flag, wait_value)
     switch (G) {
         case 8: ESP_S1(8); break;
         case 4: ESP_S1(4); break;
@@ -262,13 +323,14 @@ static int launch_stage1(float* mid_o, float* mid_lse, const void* q, const void
 
 using namespace esp;
 
-extern "C" int esp_decode_stage1(float* mid_o, float* mid_lse, const void* q, const void* k,
+static int decode_stage1_impl(float* mid_o, float* mid_lse, const void* q, const void* k,
                                  const void* v, int64_t k_stride_t, int64_t k_stride_h,
                                  int64_t v_stride_t, int64_t v_stride_h, const int32_t* req_to_tokens,
                                  int64_t req_to_tokens_stride, const int32_t* b_req_idx,
                                  const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
                                  int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
-                                 int32_t seq_block_size, int32_t dtype, float sm_scale, void* stream) {
+                                 int32_t seq_block_size, int32_t dtype, float sm_scale, void* stream,
+                                 const int32_t* wait_flag, int32_t wait_value) {
     if (batch == 0 || max_len_in_batch <= 0) return ESP_OK;
     if (!mid_o || !mid_lse || !q || !k || !v || !req_to_tokens || !b_req_idx || !b_seqlen || batch < 0 ||
         num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads || seq_block_size <= 0)
@@ -284,19 +346,46 @@ extern "C" int esp_decode_stage1(float* mid_o, float* mid_lse, const void* q, co
         return launch_stage1<__half>(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t,
                                      v_stride_h, req_to_tokens, req_to_tokens_stride, b_req_idx,
                                      b_seqlen, batch, num_q_heads, num_kv_heads, max_len_in_batch,
-                                     seq_block_size, scale, s);
+                                     seq_block_size, scale, s, wait_flag, wait_value);
     if (dtype == ESP_DTYPE_BF16)
         return launch_stage1<__nv_bfloat16>(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t,
                                             v_stride_h, req_to_tokens, req_to_tokens_stride, b_req_idx,
                                             b_seqlen, batch, num_q_heads, num_kv_heads,
-                                            max_len_in_batch, seq_block_size, scale, s);
+                                            max_len_in_batch, seq_block_size, scale, s, wait_flag, wait_value);
     return ESP_ERR_BAD_ARG;
 }
 
-extern "C" int esp_decode_merge(void* o, float* out_lse, const int32_t* b_seqlen, const float* mid_o,
+extern "C" int esp_decode_stage1(float* mid_o, float* mid_lse, const void* q, const void* k,
+                                 const void* v, int64_t k_stride_t, int64_t k_stride_h,
+                                 int64_t v_stride_t, int64_t v_stride_h, const int32_t* req_to_tokens,
+                                 int64_t req_to_tokens_stride, const int32_t* b_req_idx,
+                                 const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
+                                 int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
+                                 int32_t seq_block_size, int32_t dtype, float sm_scale, void* stream) {
+    return decode_stage1_impl(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t, v_stride_h, req_to_tokens,
+                              req_to_tokens_stride, b_req_idx, b_seqlen, batch, num_q_heads, num_kv_heads, head_dim,
+                              max_len_in_batch, seq_block_size, dtype, sm_scale, stream, nullptr, 0);
+}
+
+extern "C" int esp_decode_stage1_gated(float* mid_o, float* mid_lse, const void* q, const void* k,
+                                       const void* v, int64_t k_stride_t, int64_t k_stride_h,
+                                       int64_t v_stride_t, int64_t v_stride_h, const int32_t* req_to_tokens,
+                                       int64_t req_to_tokens_stride, const int32_t* b_req_idx,
+                                       const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
+                                       int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
+                                       int32_t seq_block_size, int32_t dtype, float sm_scale,
+                                       const int32_t* wait_flag, int32_t wait_value, void* stream) {
+    if (!wait_flag) return ESP_ERR_BAD_ARG;
+    return decode_stage1_impl(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t, v_stride_h, req_to_tokens,
+                              req_to_tokens_stride, b_req_idx, b_seqlen, batch, num_q_heads, num_kv_heads, head_dim,
+                              max_len_in_batch, seq_block_size, dtype, sm_scale, stream, wait_flag, wait_value);
+}
+
+static int decode_merge_impl(void* o, float* out_lse, const int32_t* b_seqlen, const float* mid_o,
                                 const float* mid_lse, int32_t batch, int32_t num_heads,
                                 int32_t head_dim, int32_t num_blocks, int32_t block_seq,
-                                int32_t o_dtype, void* stream) {
+                                int32_t o_dtype, void* stream, const int32_t* wait_flags, int32_t n_wait,
+                                int32_t wait_value) {
     if (batch == 0) return ESP_OK;
     if (!o || !out_lse || !b_seqlen || !mid_o || !mid_lse || batch < 0 || num_heads <= 0 ||
         num_blocks < 0 || block_seq <= 0)
@@ -309,20 +398,127 @@ extern "C" int esp_decode_merge(void* o, float* out_lse, const int32_t* b_seqlen
     switch (o_dtype) {
         case ESP_DTYPE_F32:
             decode_merge_kernel<float><<<grid, 128, 0, s>>>((float*)o, out_lse, b_seqlen, mid_o, mid_lse,
-                                                           batch, num_heads, num_blocks, block_seq);
+                                                           batch, num_heads, num_blocks, block_seq, wait_flags, n_wait, wait_value);
             break;
         case ESP_DTYPE_F16:
             decode_merge_kernel<__half><<<grid, 128, 0, s>>>((__half*)o, out_lse, b_seqlen, mid_o,
-                                                            mid_lse, batch, num_heads, num_blocks, block_seq);
+                                                            mid_lse, batch, num_heads, num_blocks, block_seq, wait_flags, n_wait, wait_value);
             break;
         case ESP_DTYPE_BF16:
             decode_merge_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>((__nv_bfloat16*)o, out_lse, b_seqlen,
                                                                    mid_o, mid_lse, batch, num_heads,
-                                                                   num_blocks, block_seq);
+                                                                   num_blocks, block_seq, wait_flags, n_wait, wait_value);
             break;
         default: return ESP_ERR_BAD_ARG;
     }
     ESP_LAUNCH_CHECK("decode_merge_kernel");
+    return ESP_OK;
+}
+
+extern "C" int esp_decode_merge(void* o, float* out_lse, const int32_t* b_seqlen, const float* mid_o,
+                                const float* mid_lse, int32_t batch, int32_t num_heads,
+                                int32_t head_dim, int32_t num_blocks, int32_t block_seq,
+                                int32_t o_dtype, void* stream) {
+    return decode_merge_impl(o, out_lse, b_seqlen, mid_o, mid_lse, batch, num_heads, head_dim, num_blocks, block_seq,
+                             o_dtype, stream, nullptr, 0, 0);
+}
+
+extern "C" int esp_decode_merge_gated(void* o, float* out_lse, const int32_t* b_seqlen, const float* mid_o,
+                                      const float* mid_lse, int32_t batch, int32_t num_heads,
+                                      int32_t head_dim, int32_t num_blocks, int32_t block_seq,
+                                      int32_t o_dtype, const int32_t* wait_flags, int32_t n_wait,
+                                      int32_t wait_value, void* stream) {
+    if (n_wait < 0 || (n_wait > 0 && !wait_flags)) return ESP_ERR_BAD_ARG;
+    return decode_merge_impl(o, out_lse, b_seqlen, mid_o, mid_lse, batch, num_heads, head_dim, num_blocks, block_seq,
+                             o_dtype, stream, n_wait > 0 ? wait_flags : nullptr, n_wait, wait_value);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Peer memory: buffers other GPUs of the node can store into directly over NVLink, a push kernel that
+// copies a block into every peer's buffer and then raises a flag there, and a one-word signal.
+namespace esp {
+constexpr int kMaxPushPeers = 16;
+struct PushTargets { void* dst[kMaxPushPeers]; int32_t* flag[kMaxPushPeers]; };
+
+// grid = number of peers; one CTA copies `bytes` (multiple of 16) into one peer and then publishes the flag
+__global__ void __launch_bounds__(1024) peer_push_kernel(const uint4* __restrict__ src, PushTargets tg, int64_t nvec, int value) {
+    uint4* dst = reinterpret_cast<uint4*>(tg.dst[blockIdx.x]);
+    for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) dst[i] = src[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_sys(tg.flag[blockIdx.x], value);
+}
+__global__ void peer_signal_kernel(int32_t* flag, int value) {
+    __threadfence_system();
+    st_release_sys(flag, value);
+}
+}  // namespace esp
+
+extern "C" int esp_peer_buffer_create(int64_t bytes, void** dev_ptr, uint8_t handle_out[64]) {
+    if (bytes <= 0 || !dev_ptr || !handle_out) return ESP_ERR_BAD_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "unexpected IPC handle size");
+    void* p = nullptr;
+    ESP_CUDA_TRY(cudaMalloc(&p, (size_t)bytes));
+    cudaError_t e = cudaMemset(p, 0, (size_t)bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) { cudaFree(p); return cuda_fail(e, "esp_peer_buffer_create"); }
+    memcpy(handle_out, &h, 64);
+    *dev_ptr = p;
+    return ESP_OK;
+}
+
+extern "C" int esp_peer_buffer_open(const uint8_t handle[64], void** dev_ptr) {
+    if (!handle || !dev_ptr) return ESP_ERR_BAD_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    ESP_CUDA_TRY(cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return ESP_OK;
+}
+
+extern "C" int esp_peer_buffer_close(void* dev_ptr) {
+    if (!dev_ptr) return ESP_ERR_BAD_ARG;
+    ESP_CUDA_TRY(cudaIpcCloseMemHandle(dev_ptr));
+    return ESP_OK;
+}
+
+extern "C" int esp_peer_buffer_destroy(void* dev_ptr) {
+    if (!dev_ptr) return ESP_ERR_BAD_ARG;
+    ESP_CUDA_TRY(cudaFree(dev_ptr));
+    return ESP_OK;
+}
+
+extern "C" int esp_peer_push(const void* src, void* const* peer_dst, int32_t* const* peer_flags, int32_t n_peers,
+                             int64_t bytes, int32_t flag_value, void* stream) {
+    if (n_peers == 0) return ESP_OK;
+    if (!src || !peer_dst || !peer_flags || n_peers < 0 || bytes < 0) return ESP_ERR_BAD_ARG;
+    if (n_peers > kMaxPushPeers) return ESP_ERR_TOO_LARGE;
+    if (bytes % 16 || !aligned16(src)) return ESP_ERR_ALIGNMENT;
+    PushTargets tg;
+    for (int i = 0; i < n_peers; ++i) {
+        if (!peer_dst[i] || !peer_flags[i] || !aligned16(peer_dst[i])) return ESP_ERR_BAD_ARG;
+        tg.dst[i] = peer_dst[i]; tg.flag[i] = peer_flags[i];
+    }
+    peer_push_kernel<<<n_peers, 1024, 0, (cudaStream_t)stream>>>((const uint4*)src, tg, bytes / 16, flag_value);
+    ESP_LAUNCH_CHECK("peer_push_kernel");
+    return ESP_OK;
+}
+
+extern "C" int esp_peer_signal(int32_t* remote_flag, int32_t value, void* stream) {
+    if (!remote_flag) return ESP_ERR_BAD_ARG;
+    peer_signal_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(remote_flag, value);
+    ESP_LAUNCH_CHECK("peer_signal_kernel");
+    return ESP_OK;
+}
+
+extern "C" int esp_decode_device_status(int32_t out[4], int32_t clear) {
+    if (!out) return ESP_ERR_BAD_ARG;
+    ESP_CUDA_TRY(cudaDeviceSynchronize());
+    ESP_CUDA_TRY(cudaMemcpyFromSymbol(out, g_decode_status, sizeof(int) * 4));
+    if (clear) {
+        int zero[4] = {0, 0, 0, 0};
+        ESP_CUDA_TRY(cudaMemcpyToSymbol(g_decode_status, zero, sizeof(zero)));
+    }
     return ESP_OK;
 }
 

@@ -347,3 +347,67 @@ def test_two_masters_two_gpus(tmp_path):
         got, want = p["o"].float(), ro[p["reqs"]]
         assert bool(((got - want).abs() <= 2e-2 + 1e-2 * want.abs()).all())
         assert torch.allclose(p["lse"], rl[p["reqs"]], atol=1e-3, rtol=1e-3)
+
+
+def _fused_decode_worker(rank, world, port, out):
+    dist, comm = _setup(rank, world, port)
+    from loongserve_b200.peer_decode import FusedDecodeGroup
+    dev = torch.device("cuda", rank)
+    g = torch.Generator().manual_seed(0)
+    B, Hh, D, bs = 4, 8, 128, 256
+    lens = [3000, 41, 1290, 640]
+    total = sum(lens)
+    kall = torch.randn(total, Hh, D, generator=g).to(torch.bfloat16); vall = torch.randn(total, Hh, D, generator=g).to(torch.bfloat16)
+    qs = [torch.randn(B, Hh, D, generator=g).to(torch.bfloat16) for _ in range(3)]
+    pool = torch.zeros(total, 2 * Hh, D, dtype=torch.bfloat16); rt = torch.full((B, 4000), O.INT32_MAX, dtype=torch.int32)
+    loc_len = []
+    off = 0; slot = 0
+    for b, L in enumerate(lens):
+        n = len(range(rank, L, world))
+        pool[slot:slot + n, :Hh] = kall[off + rank:off + L:world]; pool[slot:slot + n, Hh:] = vall[off + rank:off + L:world]
+        rt[b, :n] = torch.arange(slot, slot + n, dtype=torch.int32)
+        slot += n; loc_len.append(n); off += L
+    pool, rt = pool.to(dev), rt.to(dev)
+    b_req = torch.arange(B, dtype=torch.int32, device=dev); b_len = torch.tensor(loc_len, dtype=torch.int32, device=dev)
+    mx = max(loc_len); nblk = (mx + bs - 1) // bs
+
+    def gather(b):
+        lst = [None] * world
+        dist.all_gather_object(lst, b)
+        return lst
+
+    grp = FusedDecodeGroup(rank, world, 0, B, Hh, D, gather)
+    mid_o = torch.empty(nblk, B, Hh, D, device=dev); mid_l = torch.empty(nblk, B, Hh, device=dev)
+    res = []
+    for q in qs:                                   # three steps in a row: the flags advance 1, 2, 3
+        r = grp.step(q.to(dev) if rank == 0 else None, pool, rt, Hh, b_req, b_len, mx, bs, mid_o, mid_l)
+        if rank == 0:
+            res.append((r[0].cpu(), r[1].cpu()))
+    torch.cuda.synchronize()
+    st = grp.device_status()
+    dist.barrier()
+    if rank == 0:
+        torch.save((res, st), os.path.join(out, "fused.pt"))
+    grp.close()
+    comm.close()
+    dist.destroy_process_group()
+
+
+def test_fused_peer_memory_decode_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    mp.spawn(_fused_decode_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    res, st = torch.load(os.path.join(str(tmp_path), "fused.pt"))
+    assert st[0] == 0, f"a bounded flag wait expired: {st}"
+    g = torch.Generator().manual_seed(0)
+    B, Hh, D = 4, 8, 128
+    lens = [3000, 41, 1290, 640]; total = sum(lens)
+    kall = torch.randn(total, Hh, D, generator=g).to(torch.bfloat16); vall = torch.randn(total, Hh, D, generator=g).to(torch.bfloat16)
+    qs = [torch.randn(B, Hh, D, generator=g).to(torch.bfloat16) for _ in range(3)]
+    rt = torch.full((B, 4000), O.INT32_MAX, dtype=torch.int32); off = 0
+    for b, L in enumerate(lens):
+        rt[b, :L] = torch.arange(off, off + L, dtype=torch.int32); off += L
+    for q, (o, lse) in zip(qs, res):
+        ro, rl = O.token_decode_attention(q, kall, vall, rt, torch.arange(B, dtype=torch.int32), torch.tensor(lens, dtype=torch.int32))
+        assert torch.allclose(o.float(), ro, atol=2e-2, rtol=1e-2) and torch.allclose(lse, rl, atol=1e-3, rtol=1e-3)
