@@ -447,6 +447,73 @@ def e2e_llama(args):
         dist.destroy_process_group()
 
 
+def varlen_bench(args):
+    """Packed varlen prefill plus token-granular KV scatter on one GPU (fourth benchmark configuration at P=1):
+    16 sequences with lengths log-uniform in [1024, 262144] (seeded), bf16, 32 heads x 128, causal; then every
+    token's K/V row is scattered into shuffled pool slots.  Sampled rows are recomputed in fp32 on the device."""
+    import torch
+    from loongserve_b200 import context_attention as ca
+    from loongserve_b200 import kv_ops
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = "cuda"
+    g = torch.Generator().manual_seed(0)
+    lens = [int(round(math.exp(float(torch.rand(1, generator=g)) * (math.log(262144) - math.log(1024)) + math.log(1024)))) for _ in range(16)]
+    T = sum(lens)
+    gg = torch.Generator(device=dev).manual_seed(1)
+    q = torch.randn(T, H, D, generator=gg, device=dev, dtype=torch.bfloat16)
+    kv = torch.randn(T, 2 * H, D, generator=gg, device=dev, dtype=torch.bfloat16)
+    o = torch.empty_like(q)
+    m = torch.empty(T, H, device=dev); l = torch.empty(T, H, device=dev)
+    ln = torch.tensor(lens, dtype=torch.int32, device=dev)
+    st = torch.cumsum(ln, 0, dtype=torch.int32) - ln
+    z = torch.zeros_like(ln)
+
+    def step():
+        ca.init_attention_state(None, m, l)
+        ca.context_attention_fwd(q, kv[:, :H], kv[:, H:], o, st, ln, z, st, ln, z, 1, max(lens), m, l)
+
+    for _ in range(args.warmup):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = sum(4.0 * D * H * L * (L + 1) / 2.0 for L in lens)
+    # sampled rows against fp32 attention on the device
+    worst = 0.0
+    starts = st.tolist()
+    for b in (0, 7, 15):
+        for r in (0, lens[b] // 2, lens[b] - 1):
+            for h in (0, 31):
+                kk = kv[starts[b]:starts[b] + r + 1, h].float(); vv = kv[starts[b]:starts[b] + r + 1, H + h].float()
+                sc = (kk @ q[starts[b] + r, h].float()) * (D ** -0.5)
+                ref = torch.softmax(sc, 0) @ vv
+                worst = max(worst, float((o[starts[b] + r, h].float() - ref).abs().max()))
+    # scatter all K/V rows into shuffled slots
+    pool = torch.empty(T + 1024, 2 * H, D, dtype=torch.bfloat16, device=dev)
+    dest = torch.randperm(T + 1024, device=dev, generator=gg)[:T].to(torch.int32)
+    kv_ops.destindex_copy_kv(kv, dest, pool)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        kv_ops.destindex_copy_kv(kv, dest, pool)
+    e1.record()
+    torch.cuda.synchronize()
+    sms = e0.elapsed_time(e1) / args.steps
+    exact = bool(torch.equal(pool[dest[::997].long()], kv[::997]))
+    print(json.dumps({"metric": "varlen_prefill_attention_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                      "dtype": "bf16", "data": "synthetic", "max_abs_err_sampled_rows": worst,
+                      "scatter": {"value": T * (2 * 2 * H * D * 2 + 4) / (sms * 1e-3) / 1e9, "unit": "GB/s", "ms": sms, "bit_exact_sample": exact},
+                      "config": {"workload": f"16 packed sequences, lengths log-uniform in [1024, 262144] (seed 0): {lens}; {T} tokens, "
+                                             f"{H}x{D} bf16 causal, then all K/V rows scattered to shuffled int32 slots"},
+                      "device_status": list(ca.device_status())}), flush=True)
+
+
 def cpu_baseline(torch):
     from oracle import esp_oracle as O
     Ts = int(os.environ.get("ESP_BENCH_CPU_TOKENS", "8192"))
@@ -480,6 +547,7 @@ def main():
     ap.add_argument("--skip-extras", action="store_true", help="skip e2e / decode / cpu baseline (profiling runs)")
     ap.add_argument("--decode-only", action="store_true", help="run only the decode part (profiling runs)")
     ap.add_argument("--decode-batch", type=int, default=64)
+    ap.add_argument("--varlen", action="store_true", help="packed varlen prefill + KV scatter on one GPU instead")
     ap.add_argument("--e2e", action="store_true", help="run the end-to-end Llama-architecture configuration instead")
     ap.add_argument("--e2e-tokens", type=int, default=524288)
     ap.add_argument("--e2e-decode-steps", type=int, default=128)
@@ -487,6 +555,9 @@ def main():
     args = ap.parse_args()
     if args.e2e:
         e2e_llama(args)
+        return
+    if args.varlen:
+        varlen_bench(args)
         return
     if args.impl == "reference":
         run_reference_arm(args)
