@@ -74,7 +74,7 @@ class FusedDecodeGroup:
         self.step_id += 1
         sid = self.step_id
         batch = b_seq_len.shape[0]
-        assert batch == self.B, "the partial slots are laid out for exactly max_batch requests"
+        assert 0 < batch <= self.B, "batch exceeds the max_batch the shared region was sized for"
         Hq, D, Hkv = self.Hq, self.D, num_kv_heads
         k_cache, v_cache = pool_layer[:, :Hkv, :], pool_layer[:, Hkv:, :]
         nblk = (max_len_in_batch + block_seq - 1) // block_seq
@@ -91,17 +91,17 @@ class FusedDecodeGroup:
                                              req_to_token_indexs.stride(0), ptr(b_req_idx), ptr(b_seq_len), batch, Hq, Hkv, D,
                                              max_len_in_batch, block_seq, tag, 0.0, s), "esp_decode_stage1")
             # merge own blocks into slot [master] of the partial region, then merge the P slots
-            own_o = self.base + self.off_o + self.master * self.B * Hq * D * 4
-            own_lse = self.base + self.off_lse + self.master * self.B * Hq * 4
+            own_o = self.base + self.off_o + self.master * batch * Hq * D * 4
+            own_lse = self.base + self.off_lse + self.master * batch * Hq * 4
             _lib.check(lib.esp_decode_merge(own_o, own_lse, ptr(b_seq_len), ptr(mid_o), ptr(mid_lse), batch, Hq, D, nblk,
                                             block_seq, _lib.ESP_DTYPE_F32, s), "esp_decode_merge")
             o = torch.empty_like(q) if out is None else out
             lse = torch.empty((batch, Hq), dtype=torch.float32, device=q.device) if out_lse is None else out_lse
             if self._ones is None or self._ones.shape[0] != batch:
                 self._ones = torch.full((batch,), self.world, dtype=torch.int32, device=q.device)
-            # the P slots are laid out [P, B_max, Hq, D]: a merge over P "blocks" with batch stride B_max
+            # the P slots are laid out [P, batch, Hq, D] for this step's batch: a merge over P one-token "blocks"
             _lib.check(lib.esp_decode_merge_gated(ptr(o), ptr(lse), ptr(self._ones), self.base + self.off_o,
-                                                  self.base + self.off_lse, self.B, Hq, D, self.world, 1, dtype_tag(o),
+                                                  self.base + self.off_lse, batch, Hq, D, self.world, 1, dtype_tag(o),
                                                   self.base + self.off_flags + 4, n, sid, s), "esp_decode_merge_gated")
             return o, lse
         # ---- peer
@@ -113,7 +113,7 @@ class FusedDecodeGroup:
                    "esp_decode_stage1_gated")
         mbase = self.peer_base[self.master]
         slot = self.rank
-        _lib.check(lib.esp_decode_merge(mbase + self.off_o + slot * self.B * Hq * D * 4, mbase + self.off_lse + slot * self.B * Hq * 4,
+        _lib.check(lib.esp_decode_merge(mbase + self.off_o + slot * batch * Hq * D * 4, mbase + self.off_lse + slot * batch * Hq * 4,
                                         ptr(b_seq_len), ptr(mid_o), ptr(mid_lse), batch, Hq, D, nblk, block_seq,
                                         _lib.ESP_DTYPE_F32, s), "esp_decode_merge (remote)")
         flag_idx = 1 + self.peers.index(self.rank)

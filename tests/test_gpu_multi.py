@@ -376,7 +376,7 @@ def _fused_decode_worker(rank, world, port, out):
         dist.all_gather_object(lst, b)
         return lst
 
-    grp = FusedDecodeGroup(rank, world, 0, B, Hh, D, gather)
+    grp = FusedDecodeGroup(rank, world, 0, B + 3, Hh, D, gather)          # region sized for a larger batch than the one used
     mid_o = torch.empty(nblk, B, Hh, D, device=dev); mid_l = torch.empty(nblk, B, Hh, device=dev)
     res = []
     for q in qs:                                   # three steps in a row: the flags advance 1, 2, 3
