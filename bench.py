@@ -514,6 +514,48 @@ def varlen_bench(args):
                       "device_status": list(ca.device_status())}), flush=True)
 
 
+def ops_bench(args):
+    """The remaining HBM-bound kernels on small cases (inputs larger than L2, about 1-2 GB each): KV scatter, RMSNorm,
+    RoPE, SiLU*mul.  Prints achieved GB/s of algorithmic bytes per kernel; also the command ncu profiles."""
+    import torch
+    from loongserve_b200 import kv_ops, layer_ops
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = "cuda"
+    peaks = load_peaks()
+    g = torch.Generator(device=dev).manual_seed(0)
+    T = 65536
+    src = torch.randn(T, 2 * H, D, generator=g, device=dev, dtype=torch.bfloat16)
+    pool = torch.empty(T + 64, 2 * H, D, dtype=torch.bfloat16, device=dev)
+    dest = torch.randperm(T + 64, device=dev, generator=g)[:T].to(torch.int32)
+    x = torch.randn(T, 4096, generator=g, device=dev, dtype=torch.bfloat16); w = torch.ones(4096, device=dev, dtype=torch.bfloat16)
+    y = torch.empty_like(x)
+    q = torch.randn(T, H, D, generator=g, device=dev, dtype=torch.bfloat16)
+    cos = torch.rand(T, D // 2, generator=g, device=dev).to(torch.bfloat16); sin = torch.rand(T, D // 2, generator=g, device=dev).to(torch.bfloat16)
+    io = torch.randn(16384, 2 * 11008, generator=g, device=dev, dtype=torch.bfloat16)
+    cases = [
+        ("kv_scatter", lambda: kv_ops.destindex_copy_kv(src, dest, pool), T * (2 * 2 * H * D * 2 + 4)),
+        ("rms_norm", lambda: layer_ops.rms_norm(x, w, 1e-5, out=y), 2 * x.numel() * 2 + 4096 * 2),
+        ("rotary_emb(q and k)", lambda: layer_ops.rotary_emb(q, src[:, :H], cos, sin), 2 * (2 * q.numel() * 2 + 2 * cos.numel() * 2)),
+        ("silu_and_mul", lambda: layer_ops.silu_and_mul_inplace(io), 16384 * 11008 * 2 * 3),
+    ]
+    res = {}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, fn_, nbytes in cases:
+        for _ in range(max(args.warmup, 1)):
+            fn_()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            fn_()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        res[name] = {"ms": ms, "GB/s": gbs, "algorithmic_bytes": nbytes, "frac_of_hbm_peak": gbs / peaks["hbm"]}
+    print(json.dumps({"metric": "hbm_bound_small_kernels", "unit": "GB/s", "peak": peaks["hbm"], "peak_source": peaks["src"],
+                      "results": res}), flush=True)
+
+
 def cpu_baseline(torch):
     from oracle import esp_oracle as O
     Ts = int(os.environ.get("ESP_BENCH_CPU_TOKENS", "8192"))
@@ -547,6 +589,7 @@ def main():
     ap.add_argument("--skip-extras", action="store_true", help="skip e2e / decode / cpu baseline (profiling runs)")
     ap.add_argument("--decode-only", action="store_true", help="run only the decode part (profiling runs)")
     ap.add_argument("--decode-batch", type=int, default=64)
+    ap.add_argument("--ops-only", action="store_true", help="small cases of the scatter and element-wise kernels (profiling runs)")
     ap.add_argument("--varlen", action="store_true", help="packed varlen prefill + KV scatter on one GPU instead")
     ap.add_argument("--e2e", action="store_true", help="run the end-to-end Llama-architecture configuration instead")
     ap.add_argument("--e2e-tokens", type=int, default=524288)
@@ -558,6 +601,9 @@ def main():
         return
     if args.varlen:
         varlen_bench(args)
+        return
+    if args.ops_only:
+        ops_bench(args)
         return
     if args.impl == "reference":
         run_reference_arm(args)

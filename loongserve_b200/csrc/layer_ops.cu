@@ -74,26 +74,41 @@ __global__ void __launch_bounds__(256) rotary_kernel(T* __restrict__ x, const T*
                                                      int64_t stride_t, int64_t stride_h, int64_t tokens, int heads, int head_dim) {
     const int vec_per_head = head_dim >> 4;                  // 16-byte vectors in half a head
     const int64_t total = tokens * heads * vec_per_head;
-    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-        const int v = (int)(idx % vec_per_head);
-        const int64_t th = idx / vec_per_head;
-        const int h = (int)(th % heads);
-        const int64_t t = th / heads;
-        T* base = x + t * stride_t + (int64_t)h * stride_h + v * 8;
-        const uint4 a = *reinterpret_cast<const uint4*>(base);
-        const uint4 b = *reinterpret_cast<const uint4*>(base + head_dim / 2);
-        const uint4 c = *reinterpret_cast<const uint4*>(cosv + t * (head_dim / 2) + v * 8);
-        const uint4 s = *reinterpret_cast<const uint4*>(sinv + t * (head_dim / 2) + v * 8);
-        const uint32_t ua[4] = {a.x, a.y, a.z, a.w}, ub[4] = {b.x, b.y, b.z, b.w}, uc[4] = {c.x, c.y, c.z, c.w}, us[4] = {s.x, s.y, s.z, s.w};
-        uint32_t ra[4], rb[4];
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    // two work items per thread and iteration: eight 16-byte loads in flight before the first store
+    for (int64_t idx0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx0 < total; idx0 += 2 * stride) {
+        T* base[2]; uint4 a[2], b[2], c[2], sn[2]; bool on[2];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float2 x1 = Cvt<T>::to_f2(ua[k]), x2 = Cvt<T>::to_f2(ub[k]), cc = Cvt<T>::to_f2(uc[k]), sn = Cvt<T>::to_f2(us[k]);
-            ra[k] = Cvt<T>::pack(x1.x * cc.x - x2.x * sn.x, x1.y * cc.y - x2.y * sn.y);
-            rb[k] = Cvt<T>::pack(x1.x * sn.x + x2.x * cc.x, x1.y * sn.y + x2.y * cc.y);
+        for (int u = 0; u < 2; ++u) {
+            const int64_t idx = idx0 + u * stride;
+            on[u] = idx < total;
+            if (on[u]) {
+                const int v = (int)(idx % vec_per_head);
+                const int64_t th = idx / vec_per_head;
+                const int h = (int)(th % heads);
+                const int64_t t = th / heads;
+                base[u] = x + t * stride_t + (int64_t)h * stride_h + v * 8;
+                a[u] = *reinterpret_cast<const uint4*>(base[u]);
+                b[u] = *reinterpret_cast<const uint4*>(base[u] + head_dim / 2);
+                c[u] = *reinterpret_cast<const uint4*>(cosv + t * (head_dim / 2) + v * 8);
+                sn[u] = *reinterpret_cast<const uint4*>(sinv + t * (head_dim / 2) + v * 8);
+            }
         }
-        *reinterpret_cast<uint4*>(base) = make_uint4(ra[0], ra[1], ra[2], ra[3]);
-        *reinterpret_cast<uint4*>(base + head_dim / 2) = make_uint4(rb[0], rb[1], rb[2], rb[3]);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (!on[u]) continue;
+            const uint32_t ua[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, ub[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+            const uint32_t uc[4] = {c[u].x, c[u].y, c[u].z, c[u].w}, us[4] = {sn[u].x, sn[u].y, sn[u].z, sn[u].w};
+            uint32_t ra[4], rb[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 x1 = Cvt<T>::to_f2(ua[k]), x2 = Cvt<T>::to_f2(ub[k]), cc = Cvt<T>::to_f2(uc[k]), ss = Cvt<T>::to_f2(us[k]);
+                ra[k] = Cvt<T>::pack(x1.x * cc.x - x2.x * ss.x, x1.y * cc.y - x2.y * ss.y);
+                rb[k] = Cvt<T>::pack(x1.x * ss.x + x2.x * cc.x, x1.y * ss.y + x2.y * cc.y);
+            }
+            *reinterpret_cast<uint4*>(base[u]) = make_uint4(ra[0], ra[1], ra[2], ra[3]);
+            *reinterpret_cast<uint4*>(base[u] + head_dim / 2) = make_uint4(rb[0], rb[1], rb[2], rb[3]);
+        }
     }
 }
 
@@ -101,20 +116,34 @@ template <typename T>
 __global__ void __launch_bounds__(256) silu_mul_kernel(T* __restrict__ io, int64_t tokens, int ffn) {
     const int vec = ffn >> 3;
     const int64_t total = tokens * vec;
-    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t t = idx / vec;
-        const int v = (int)(idx - t * vec);
-        T* g = io + t * (2 * (int64_t)ffn) + v * 8;
-        const uint4 a = *reinterpret_cast<const uint4*>(g);
-        const uint4 b = *reinterpret_cast<const uint4*>(g + ffn);
-        const uint32_t ua[4] = {a.x, a.y, a.z, a.w}, ub[4] = {b.x, b.y, b.z, b.w};
-        uint32_t r[4];
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    // two independent vectors per thread and iteration: four 16-byte loads in flight before the first store
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += 2 * stride) {
+        T* g[2]; uint4 a[2], b[2]; bool on[2];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float2 x = Cvt<T>::to_f2(ua[k]), u = Cvt<T>::to_f2(ub[k]);
-            r[k] = Cvt<T>::pack(x.x / (1.f + __expf(-x.x)) * u.x, x.y / (1.f + __expf(-x.y)) * u.y);
+        for (int u = 0; u < 2; ++u) {
+            const int64_t id = idx + u * stride;
+            on[u] = id < total;
+            if (on[u]) {
+                const int64_t t = id / vec;
+                const int v = (int)(id - t * vec);
+                g[u] = io + t * (2 * (int64_t)ffn) + v * 8;
+                a[u] = *reinterpret_cast<const uint4*>(g[u]);
+                b[u] = *reinterpret_cast<const uint4*>(g[u] + ffn);
+            }
         }
-        *reinterpret_cast<uint4*>(g) = make_uint4(r[0], r[1], r[2], r[3]);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (!on[u]) continue;
+            const uint32_t ua[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, ub[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+            uint32_t r[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 x = Cvt<T>::to_f2(ua[k]), up = Cvt<T>::to_f2(ub[k]);
+                r[k] = Cvt<T>::pack(x.x / (1.f + __expf(-x.x)) * up.x, x.y / (1.f + __expf(-x.y)) * up.y);
+            }
+            *reinterpret_cast<uint4*>(g[u]) = make_uint4(r[0], r[1], r[2], r[3]);
+        }
     }
 }
 
