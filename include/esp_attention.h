@@ -244,6 +244,24 @@ int esp_mig_scatter(const void* recv_buf, int64_t total_tokens, int32_t* req_to_
                     int32_t elem_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Host-side slot allocator with the allocation order of LongServeMemoryManager
+ *   (loongserve/common/longserve_mem_manager.py:32-89): lowest free ids first, first free run for contiguous
+ * requests, int32 reference counts -- kept entirely on the host (bitmap), so no device synchronisation.
+ * esp_pool_alloc returns ESP_ERR_TOO_LARGE when fewer than n slots are free (the reference asserts);
+ * esp_pool_alloc_contiguous stores -1 in *start when no run of n free slots exists (the reference returns None).
+ */
+typedef struct esp_pool esp_pool;
+int esp_pool_create(int64_t size, esp_pool** out);
+int esp_pool_destroy(esp_pool* pool);
+int64_t esp_pool_can_use(const esp_pool* pool);
+int esp_pool_alloc(esp_pool* pool, int64_t n, int64_t* out_ids);
+int esp_pool_alloc_contiguous(esp_pool* pool, int64_t n, int64_t* start);
+int esp_pool_add_refs(esp_pool* pool, const int64_t* ids, int64_t n);
+int esp_pool_decrease_refs(esp_pool* pool, const int64_t* ids, int64_t n);
+int esp_pool_free_all(esp_pool* pool);
+int esp_pool_state(const esp_pool* pool, int32_t* out_refcounts);
+
+/* ------------------------------------------------------------------------------------------------
  * Element-wise layer kernels around the attention path (needed only to run a whole Llama layer).
  */
 

@@ -50,6 +50,14 @@ ATTN_SIGNATURES = {
                        _i32, _i32, _i32, _vp],
     "esp_mig_scatter": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32,
                         _i32, _i32, _i32, _i32, _vp],
+    "esp_pool_create": [_i64, C.POINTER(_vp)],
+    "esp_pool_destroy": [_vp],
+    "esp_pool_alloc": [_vp, _i64, _vp],
+    "esp_pool_alloc_contiguous": [_vp, _i64, C.POINTER(_i64)],
+    "esp_pool_add_refs": [_vp, _vp, _i64],
+    "esp_pool_decrease_refs": [_vp, _vp, _i64],
+    "esp_pool_free_all": [_vp],
+    "esp_pool_state": [_vp, _vp],
     "esp_rms_norm": [_vp, _vp, _vp, _i64, _i32, _f32, _i32, _vp],
     "esp_rotary_emb": [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _vp],
     "esp_silu_and_mul_inplace": [_vp, _i64, _i32, _i32, _vp],
@@ -89,6 +97,8 @@ def attn():
             fn = getattr(lib, name)
             fn.argtypes = args
             fn.restype = C.c_char_p
+        lib.esp_pool_can_use.argtypes = [_vp]
+        lib.esp_pool_can_use.restype = _i64
         _attn = lib
     return _attn
 

@@ -18,7 +18,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 ROOT = os.path.dirname(HERE)
 
-ATTN_SOURCES = ["kv_scatter.cu", "decode_attention.cu", "prefill_attention.cu", "selftest_umma.cu", "layer_ops.cu"]
+ATTN_SOURCES = ["kv_scatter.cu", "decode_attention.cu", "prefill_attention.cu", "selftest_umma.cu", "layer_ops.cu",
+                "pool_allocator.cpp"]
 ATTN_LIB = os.path.join(HERE, "libesp_attention.so")
 RNCCL_LIB = os.path.join(HERE, "libesp_rnccl.so")
 

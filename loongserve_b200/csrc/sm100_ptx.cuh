@@ -14,6 +14,11 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 }
 
 // ---------------------------------------------------------------- mbarrier
+// Upper bound (ns) a try_wait may keep the warp suspended before it returns false; the warp still wakes as soon as the
+// phase completes.  A long hint keeps waiting warps out of the issue slots.
+#ifndef ESP_MBAR_SUSPEND_HINT_NS
+#define ESP_MBAR_SUSPEND_HINT_NS 1000000u
+#endif
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -33,9 +38,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(ESP_MBAR_SUSPEND_HINT_NS) : "memory");
     return ok != 0;
 }
 

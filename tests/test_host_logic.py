@@ -182,3 +182,57 @@ def test_multi_master_decode_world2_gloo(tmp_path):
         rt[b, :L] = torch.arange(off, off + L, dtype=torch.int32); off += L
     ro, rl = O.token_decode_attention(q, kall, vall, rt, torch.arange(B, dtype=torch.int32), torch.tensor(lens, dtype=torch.int32))
     assert torch.allclose(o, ro, atol=1e-5, rtol=1e-5) and torch.allclose(lse, rl, atol=1e-5, rtol=1e-5)
+
+
+def test_host_side_allocator_matches_reference_trace_and_oracle(golden_dir):
+    """The native host allocator reproduces the reference-generated golden trace and, over a random sequence of
+    operations, the oracle's restatement of the reference allocator, slot for slot."""
+    from loongserve_b200.mem_manager import HostSlotAllocator, SyncFreeMemoryManager
+    g = np.load(os.path.join(golden_dir, "mem_manager.npz"))
+    mm = SyncFreeMemoryManager(64, torch.float16, 2, 8, 1, device="cpu")
+    a = mm.alloc(5)
+    assert np.array_equal(a.numpy(), g["t0_alloc5"]) and mm.can_use_mem_size == int(g["t0_free"])
+    b = mm.alloc_contiguous(7)
+    assert np.array_equal(b[0].numpy(), g["t1_contig7"]) and mm.can_use_mem_size == int(g["t1_free"])
+    mm.free(a[1:4])
+    assert np.array_equal(mm.mem_state.numpy(), g["t2_free_a1_4"]) and mm.can_use_mem_size == int(g["t2_free"])
+    c = mm.alloc(6)
+    assert np.array_equal(c.numpy(), g["t3_alloc6"]) and mm.can_use_mem_size == int(g["t3_free"])
+    d = mm.alloc_contiguous(4)
+    assert np.array_equal(d[0].numpy(), g["t4_contig4"]) and mm.can_use_mem_size == int(g["t4_free"])
+    mm.add_refs(c[:2])
+    assert np.array_equal(mm.mem_state.numpy(), g["t5_addref"]) and mm.can_use_mem_size == int(g["t5_free"])
+    mm.free(c)
+    assert np.array_equal(mm.mem_state.numpy(), g["t6_free_c"]) and mm.can_use_mem_size == int(g["t6_free"])
+    assert mm.alloc_contiguous(60) is None
+    with pytest.raises(RuntimeError, match="not enough KV cache"):
+        mm.alloc(10_000)
+    assert np.array_equal(mm._host.state().numpy(), mm.mem_state.numpy())
+    # randomised comparison with the oracle
+    rng = np.random.default_rng(0)
+    size = 700
+    host = HostSlotAllocator(size); ora = O.OracleMemoryManager(size)
+    held = []
+    for step in range(400):
+        op = rng.integers(0, 4)
+        if op == 0 and ora.can_use_mem_size > 0:
+            n = int(rng.integers(1, min(40, ora.can_use_mem_size) + 1))
+            x = host.alloc(n).numpy(); y = ora.alloc(n)
+            assert np.array_equal(x, y); held.append(y)
+        elif op == 1:
+            n = int(rng.integers(1, 60))
+            x = host.alloc_contiguous(n); y = ora.alloc_contiguous(n)
+            assert (x is None) == (y is None)
+            if y is not None:
+                assert x == y[1]; held.append(y[0])
+        elif op == 2 and held:
+            ids = held.pop(int(rng.integers(0, len(held))))
+            host.decrease_refs(torch.from_numpy(ids)); ora.decrease_refs(ids)
+        elif op == 3 and held:
+            ids = held[int(rng.integers(0, len(held)))][:3]
+            host.add_refs(torch.from_numpy(ids)); ora.add_refs(ids)
+            held.append(ids)
+        assert host.can_use == ora.can_use_mem_size
+        if step % 50 == 0:
+            assert np.array_equal(host.state().numpy(), ora.mem_state)
+    assert np.array_equal(host.state().numpy(), ora.mem_state)
