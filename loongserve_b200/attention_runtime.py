@@ -101,14 +101,67 @@ class ESPAttentionRuntime:
             local_len, first, stride = ringmod.shard_lengths(request_lengths, P, striped)
             st.block_metas = [ringmod.BlockMeta.from_lengths(local_len[r], first[r], self.device) for r in range(P)]
             st.stride = stride
-        else:
-            assert P == 1, "request_lengths is required when the batch spans several instances"
+        elif P == 1:
             st.block_metas = [ringmod.BlockMeta(b_start_loc, b_seq_len, first_token_global_idx)]
             st.stride = 1
+        else:
+            # no host knowledge of the other instances' shards: pass the metadata round the ring once per batch
+            # (the reference sends it along with every KV block of every layer,
+            # longserve_transformer_layer_infer.py:162-178)
+            st.block_metas = self._exchange_block_metas(b_start_loc, b_seq_len, first_token_global_idx,
+                                                        st.logical_sp_peer_ranks, logical_sp_rank)
+            st.stride = P if striped else 1
         if need_context_migration:
             st.keep_plan = ringmod.KeepPlan(kv_cache_index_begin, kv_cache_index_end, st.mem_index, b_req_idx,
                                             self.req_manager.req_to_token_indexs, st.cur_kv_cache_index)
         return st
+
+    def _exchange_block_metas(self, b_start_loc, b_seq_len, first_token_global_idx, peers, rank):
+        P = len(peers)
+        mine = torch.stack([b_start_loc, b_seq_len, first_token_global_idx]).to(torch.int32).contiguous()
+        metas = [None] * P
+        metas[rank] = mine
+        cur = mine
+        nxt, prv = peers[(rank + 1) % P], peers[(rank - 1 + P) % P]
+        for i in range(1, P):
+            recv = torch.empty_like(mine)
+            self.sp_comm.wait_for_default_stream()
+            self.sp_comm.nccl_group_start()
+            self.sp_comm.nccl_recv(recv, prv)
+            self.sp_comm.nccl_send(cur, nxt)
+            self.sp_comm.nccl_group_end()
+            self.sp_comm.let_default_stream_wait()
+            metas[(rank - i) % P] = recv
+            cur = recv
+        return [ringmod.BlockMeta(m[0], m[1], m[2]) for m in metas]
+
+    def migrate_chunked(self, is_receiver: bool, req_indices, migration_lens, seq_lens, peer_sp_rank: int, max_mig_len: int):
+        """Decode-stage migration of a list of requests in chunks of at most ``max_mig_len`` tokens, in the order
+        and with the bookkeeping of the reference's worker shell
+        (loongserve/longserve_server/router/model_infer/model_rpc.py:178-217): requests are taken from the END of
+        the lists; a request larger than the remaining buffer is split and its rest re-queued; the local length of a
+        request grows (receiver) or shrinks (sender) by each chunk.  ``seq_lens`` is updated in place and returned."""
+        req_indices, migration_lens, seq_lens = list(req_indices), list(migration_lens), list(seq_lens)
+        lens_by_req = dict(zip(req_indices, seq_lens))
+        pending = list(zip(req_indices, migration_lens))
+        while pending:
+            room = max_mig_len
+            b_req, b_mig, b_len = [], [], []
+            while pending and room > 0:
+                rid, mig = pending.pop()
+                cur = min(room, mig)
+                room -= cur
+                mig -= cur
+                b_req.append(rid); b_mig.append(cur); b_len.append(lens_by_req[rid])
+                lens_by_req[rid] += cur if is_receiver else -cur
+                if room == 0:
+                    if mig > 0:
+                        pending.append((rid, mig))
+                    break
+            i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=self.device)
+            self.decoding_stage_migration(is_receiver, i32(b_req), i32(b_mig), i32(b_len), peer_sp_rank,
+                                          migration_len_sum=sum(b_mig), max_migration_len=max(b_mig))
+        return [lens_by_req[r] for r in req_indices]
 
     def pre_cache_kv(self, st, layer_idx: int):
         """Buffer the layer's new K/V rows must be written into: the pool slice itself when the slots are

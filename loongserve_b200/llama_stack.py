@@ -117,6 +117,37 @@ class LlamaESPStack:
                 rt.token_attention(None, st, li)
         return self._logits(x) if is_master else None
 
+    # ------------------------------------------------------------------ the reference's call surface
+    @torch.inference_mode()
+    def forward(self, batch_size, total_token_num, max_token_num, max_len_in_batch, input_ids, b_req_idx, b_start_loc,
+                b_seq_len, first_token_global_idx, sp_master_rank, logical_sp_peer_ranks, logical_sp_rank,
+                newkv_alloc_sp_rank=None, peer_sp_master_rank_list=None, peer_query_buffer_range_list=None,
+                peer_batch_size=None, peer_max_len_in_batch=None, peer_b_req_idx=None, peer_b_seq_len=None,
+                need_context_migration=False, kv_cache_index_begin=None, kv_cache_index_end=None, multimodal_params=None,
+                is_prefill=True):
+        """Same keyword arguments as ``LongServeLlamaModel.forward`` (loongserve/models/llama/longserve_model.py:279-321),
+        as built by the worker's ``prepare_prefill_inputs`` / ``prepare_decode_inputs``.  Prefill returns the logits of
+        every request's last local token (longserve_post_layer_infer.py:37-43), decode the logits on the master."""
+        rt = self.rt
+        P = len(logical_sp_peer_ranks)
+        if is_prefill:
+            st = rt.prepare_prefill(batch_size, total_token_num, max_token_num, max_len_in_batch, b_req_idx, b_start_loc, b_seq_len,
+                                    first_token_global_idx, logical_sp_peer_ranks, logical_sp_rank, need_context_migration,
+                                    kv_cache_index_begin, kv_cache_index_end, striped=True)
+            # global position of local row i of a request = first + i * P (longserve_infer_struct.py:112-126)
+            lens64 = b_seq_len.long()
+            req_of_tok = torch.repeat_interleave(torch.arange(batch_size, device=lens64.device), lens64)
+            local = torch.arange(total_token_num, device=lens64.device) - b_start_loc.long()[req_of_tok]
+            positions = first_token_global_idx.long()[req_of_tok] + local * P
+            last_rows = (b_start_loc.long() + lens64 - 1).clamp_min(0)
+            return self.prefill(input_ids, positions, st, last_token_rows=last_rows)
+        is_master = sp_master_rank == rt.total_rank_
+        st = rt.prepare_decode(batch_size, total_token_num, max_len_in_batch, b_req_idx, b_seq_len, first_token_global_idx,
+                               sp_master_rank, logical_sp_peer_ranks, logical_sp_rank, peer_sp_master_rank_list,
+                               peer_query_buffer_range_list, peer_batch_size or 0, peer_max_len_in_batch or 0, peer_b_req_idx,
+                               peer_b_seq_len)
+        return self.decode(input_ids if is_master else None, first_token_global_idx if is_master else None, st)
+
     def _logits(self, x):
         h = layer_ops.rms_norm(x.contiguous(), self.w.final_norm, self.cfg.rms_eps)
         return torch.mm(h, self.w.lm_head).float()

@@ -411,3 +411,75 @@ def test_fused_peer_memory_decode_two_gpus(tmp_path):
     for q, (o, lse) in zip(qs, res):
         ro, rl = O.token_decode_attention(q, kall, vall, rt, torch.arange(B, dtype=torch.int32), torch.tensor(lens, dtype=torch.int32))
         assert torch.allclose(o.float(), ro, atol=2e-2, rtol=1e-2) and torch.allclose(lse, rl, atol=1e-3, rtol=1e-3)
+
+
+def _forward_kwargs_worker(rank, world, port, out):
+    """Drive the layer stack with exactly the keyword arguments the reference's worker builds
+    (pre_process.py:95-121 for prefill, :232-258 for decode)."""
+    dist, comm = _setup(rank, world, port)
+    from loongserve_b200.attention_runtime import ESPAttentionRuntime
+    from loongserve_b200.llama_stack import LlamaConfig, LlamaESPStack, LlamaWeights
+    dev = torch.device("cuda", rank)
+    cfg = LlamaConfig(num_layers=2, hidden=512, num_q_heads=4, num_kv_heads=4, head_dim=128, ffn=1024, vocab=1000)
+    rt = ESPAttentionRuntime(layers_num=2, q_head_num=4, kv_head_num=4, head_dim=128, max_total_token_num=2048, max_req_num=8,
+                             max_seq_length=2048, sp_world_size=world, total_rank=rank, sp_comm=comm, dtype=torch.bfloat16, device=dev,
+                             host_side_allocator=True)
+    stack = LlamaESPStack(cfg, LlamaWeights(cfg, torch.bfloat16, dev, seed=3), rt)
+    g = torch.Generator().manual_seed(9)
+    full = [301, 64, 130]
+    B = len(full)
+    ids = torch.randint(0, cfg.vocab, (sum(full),), generator=g)
+    pre = [n - 1 for n in full]
+    starts = [0, full[0], full[0] + full[1]]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    local = [list(range(rank, n, world)) for n in pre]                      # striped placement of the prompt tokens
+    local_ids = torch.cat([ids[s + torch.tensor(l, dtype=torch.long)] for s, l in zip(starts, local)]).to(dev)
+    b_len = [len(l) for l in local]
+    max_tok = max(sum(len(range(r, n, world)) for n in pre) for r in range(world))
+    kwargs = dict(batch_size=B, total_token_num=sum(b_len), max_token_num=max_tok, max_len_in_batch=max(b_len), input_ids=local_ids,
+                  b_req_idx=i32([0, 1, 2]), b_start_loc=i32([0, b_len[0], b_len[0] + b_len[1]]), b_seq_len=i32(b_len),
+                  first_token_global_idx=i32([rank] * B), sp_master_rank=None, logical_sp_peer_ranks=list(range(world)),
+                  logical_sp_rank=rank, newkv_alloc_sp_rank=None, peer_sp_master_rank_list=None, peer_query_buffer_range_list=None,
+                  peer_batch_size=None, peer_max_len_in_batch=None, peer_b_req_idx=None, peer_b_seq_len=None,
+                  need_context_migration=False, kv_cache_index_begin=None, kv_cache_index_end=None, multimodal_params=None, is_prefill=True)
+    pre_logits = stack.forward(**kwargs)
+    # decode: instance 0 is the master of all three requests
+    new_ids = torch.stack([ids[s + n - 1] for s, n in zip(starts, full)]).to(dev)
+    if rank == 0:
+        dk = dict(batch_size=B, total_token_num=B, max_token_num=None, max_len_in_batch=max(b_len) + 1, input_ids=new_ids,
+                  b_req_idx=i32([0, 1, 2]), b_start_loc=None, b_seq_len=i32([x + 1 for x in b_len]), first_token_global_idx=i32(pre),
+                  sp_master_rank=0, logical_sp_peer_ranks=list(range(world)), logical_sp_rank=0, is_prefill=False)
+    else:
+        dk = dict(batch_size=0, total_token_num=0, max_token_num=None, max_len_in_batch=0, input_ids=None, b_req_idx=None, b_start_loc=None,
+                  b_seq_len=None, first_token_global_idx=None, sp_master_rank=None, logical_sp_peer_ranks=list(range(world)),
+                  logical_sp_rank=rank, peer_sp_master_rank_list=[0], peer_query_buffer_range_list=[(0, B)], peer_batch_size=B,
+                  peer_max_len_in_batch=max(b_len), peer_b_req_idx=i32([0, 1, 2]), peer_b_seq_len=i32(b_len), is_prefill=False)
+    dec_logits = stack.forward(**dk)
+    torch.cuda.synchronize()
+    torch.save(dict(pre=pre_logits.cpu(), dec=None if dec_logits is None else dec_logits.cpu()), os.path.join(out, f"fw{rank}.pt"))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+
+
+def test_forward_with_reference_kwargs_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    mp.spawn(_forward_kwargs_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    from loongserve_b200.llama_stack import LlamaConfig, LlamaWeights
+    cfg = LlamaConfig(num_layers=2, hidden=512, num_q_heads=4, num_kv_heads=4, head_dim=128, ffn=1024, vocab=1000)
+    w = LlamaWeights(cfg, torch.bfloat16, "cuda:0", seed=3)
+    g = torch.Generator().manual_seed(9)
+    full = [301, 64, 130]
+    ids = torch.randint(0, cfg.vocab, (sum(full),), generator=g)
+    pos = torch.cat([torch.arange(n) for n in full])
+    x = w.embed.cpu()[ids.long()].float()
+    for lw in w.layers:
+        x, _, _ = O.llama_layer(x, pos, full, {k: v.cpu() for k, v in lw.items()}, cfg.rms_eps, 4, 4, 128, torch.bfloat16)
+    starts = [0, full[0], full[0] + full[1]]
+    new_rows = torch.tensor([s + n - 1 for s, n in zip(starts, full)])
+    ref = O.rms_norm(x[new_rows], w.final_norm.cpu(), cfg.rms_eps).to(torch.bfloat16).float() @ w.lm_head.cpu().float()
+    dec = torch.load(os.path.join(str(tmp_path), "fw0.pt"))["dec"]
+    err = (dec - ref).abs()
+    assert bool((err <= 5e-2 + 5e-2 * ref.abs()).all()), err.max()

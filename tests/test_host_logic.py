@@ -236,3 +236,26 @@ def test_host_side_allocator_matches_reference_trace_and_oracle(golden_dir):
         if step % 50 == 0:
             assert np.array_equal(host.state().numpy(), ora.mem_state)
     assert np.array_equal(host.state().numpy(), ora.mem_state)
+
+
+def test_migration_chunker_order_and_bookkeeping():
+    """The chunker takes requests from the end of the lists, splits at the buffer size and re-queues the rest, and
+    adjusts the local lengths, as the reference's worker shell does (model_rpc.py:178-217)."""
+    from loongserve_b200.attention_runtime import ESPAttentionRuntime
+    calls = []
+
+    class Fake(ESPAttentionRuntime):
+        def __init__(self):
+            self.device = torch.device("cpu")
+
+        def decoding_stage_migration(self, is_receiver, b_req_idx, b_migration_len, b_seq_len, peer, migration_len_sum=None,
+                                     max_migration_len=None):
+            calls.append((b_req_idx.tolist(), b_migration_len.tolist(), b_seq_len.tolist(), migration_len_sum, max_migration_len))
+
+    rt = Fake()
+    out = rt.migrate_chunked(False, [7, 3, 5], [10, 25, 4], [100, 200, 50], 1, max_mig_len=16)
+    assert calls == [([5, 3], [4, 12], [50, 200], 16, 12), ([3, 7], [13, 3], [188, 100], 16, 13), ([7], [7], [97], 7, 7)]
+    assert out == [90, 175, 46]
+    calls.clear()
+    out = rt.migrate_chunked(True, [1], [5], [9], 0, max_mig_len=100)
+    assert calls == [([1], [5], [9], 5, 5)] and out == [14]
