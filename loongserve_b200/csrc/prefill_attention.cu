@@ -602,6 +602,16 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
                           const PrefillParams& pp, dim3 grid, cudaStream_t s) {
     // set on every launch: the attribute is per device and a process may drive several
     ESP_CUDA_TRY(cudaFuncSetAttribute(prefill_step_kernel<T, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+    if (kUseSetMaxNReg) {
+        // the in-kernel register re-distribution (256 softmax threads x 224 + 128 other threads x 56) must fit the
+        // registers the CTA is launched with, or setmaxnreg.inc would block
+        cudaFuncAttributes fa;
+        ESP_CUDA_TRY(cudaFuncGetAttributes(&fa, prefill_step_kernel<T, OT>));
+        if (fa.numRegs * NUM_THREADS < 256 * 224 + 128 * 56) {
+            snprintf(last_cuda_error_buf(), 256, "prefill kernel was built with %d registers per thread, too few for its setmaxnreg plan", fa.numRegs);
+            return ESP_ERR_UNSUPPORTED;
+        }
+    }
     prefill_step_kernel<T, OT><<<grid, NUM_THREADS, SMEM_DYN, s>>>(tq, tk, tv, pp);
     ESP_LAUNCH_CHECK("prefill_step_kernel");
     return ESP_OK;
