@@ -52,6 +52,7 @@ class FusedDecodeGroup:
                 _lib.check(lib.esp_peer_buffer_open(hb, C.byref(p)), "esp_peer_buffer_open")
                 self.peer_base[r] = p.value
         self.step_id = 0
+        self._ones = None
         self.peers = [r for r in range(world) if r != master]
 
     def close(self):
@@ -119,8 +120,6 @@ class FusedDecodeGroup:
         flag_idx = 1 + self.peers.index(self.rank)
         _lib.check(lib.esp_peer_signal(mbase + self.off_flags + 4 * flag_idx, sid, s), "esp_peer_signal")
         return None
-
-    _ones = None
 
     def device_status(self, clear: bool = True):
         """(code, block, which wait, value) of the bounded flag waits on this device; code 0 = none expired."""
