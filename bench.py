@@ -376,6 +376,12 @@ def e2e_llama(args):
                              max_seq_length=max_tok + steps + 64, sp_world_size=P, total_rank=rank, sp_comm=comm,
                              dtype=torch.bfloat16, device=dev, decode_block_seq=1024)
     stack = LlamaESPStack(cfg, LlamaWeights(cfg, torch.bfloat16, dev, seed=0), rt)
+    if args.e2e_exchange == "peer_memory" and world > 1:
+        def gather(b):
+            lst = [None] * world
+            dist.all_gather_object(lst, b)
+            return lst
+        rt.enable_peer_memory_decode(0, gather, max_batch=1)
     g = torch.Generator(device=dev).manual_seed(7)
     ids_all = torch.randint(0, cfg.vocab, (T,), generator=g, device=dev)        # same stream on every rank
     ids = ids_all[rank::P].contiguous()
@@ -427,6 +433,7 @@ def e2e_llama(args):
             stack.decode(None, None, dst)
     d1.record()
     torch.cuda.synchronize()
+    last_logit_sum = float(lg.double().abs().sum()) if (rank == 0 and steps > 0) else 0.0
     t = torch.tensor([p0.elapsed_time(p1), d0.elapsed_time(d1) / max(steps, 1), 0.0 if finite else 1.0], device=dev)
     if world > 1:
         dist.barrier()
@@ -437,12 +444,15 @@ def e2e_llama(args):
         print(json.dumps({
             "metric": "e2e_llama_prefill_tokens_per_s", "value": T / (pre_ms * 1e-3), "unit": "tokens/s", "n_gpus": P,
             "prefill_ms": pre_ms, "decode_ms_per_step": dec_ms, "decode_steps": steps, "higher_is_better": True,
-            "dtype": "bf16", "data": "synthetic", "outputs_finite": bad == 0.0,
+            "dtype": "bf16", "data": "synthetic", "outputs_finite": bad == 0.0, "decode_exchange": args.e2e_exchange,
+            "last_logits_checksum": float(last_logit_sum),
             "prefill_attention_tflops_equiv": attn_flops / (pre_ms * 1e-3) / 1e12,
             "config": {"workload": f"Llama-2-7B architecture ({cfg.num_layers} layers, hidden {cfg.hidden}, {cfg.num_q_heads} heads x {cfg.head_dim}, "
                                    f"FFN {cfg.ffn}, vocab {cfg.vocab}), random-init bf16 weights; one {T}-token prefill at ESP={P} (striped), "
                                    f"then {steps} decode steps with the KV distributed over all {P} GPUs"}}), flush=True)
     if world > 1:
+        dist.barrier()
+        rt.close()
         comm.close()
         dist.destroy_process_group()
 
@@ -595,6 +605,8 @@ def main():
     ap.add_argument("--e2e-tokens", type=int, default=524288)
     ap.add_argument("--e2e-decode-steps", type=int, default=128)
     ap.add_argument("--e2e-layers", type=int, default=32)
+    ap.add_argument("--e2e-exchange", default="nccl", choices=["nccl", "peer_memory"],
+                    help="decode exchange of the end-to-end run: NCCL messages or NVLink stores + flags in the kernels")
     args = ap.parse_args()
     if args.e2e:
         e2e_llama(args)

@@ -57,6 +57,20 @@ class ESPAttentionRuntime:
         self.mem_manager = mm_cls(max_total_token_num, dtype, kv_head_num, head_dim, layers_num,
                                   num_idle_slots=sp_world_size, device=device)
         self.req_manager = LongServeReqManager(max_req_num, max_seq_length, self.mem_manager)
+        self._fused_groups = {}
+
+    def enable_peer_memory_decode(self, master_rank: int, all_gather_bytes, max_batch: int):
+        """Use NVLink stores and flags inside the kernels (``peer_decode.FusedDecodeGroup``) instead of NCCL messages
+        for decode batches whose only master is ``master_rank`` and whose peers are all instances.  Collective:
+        every instance must call it, with an ``all_gather_bytes`` that returns each rank's bytes in rank order."""
+        from .peer_decode import FusedDecodeGroup
+        self._fused_groups[master_rank] = FusedDecodeGroup(self.total_rank_, self.sp_world_size, master_rank, max_batch,
+                                                           self.tp_q_head_num_, self.head_dim_, all_gather_bytes, self.dtype)
+
+    def close(self):
+        for g in self._fused_groups.values():
+            g.close()
+        self._fused_groups = {}
 
     # ------------------------------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -292,9 +306,37 @@ class ESPAttentionRuntime:
                                      mp.global_mid_o, mp.global_mid_lse, mp.block_seq)
             return o
         qv = q.view(-1, self.tp_q_head_num_, self.head_dim_) if q is not None else None
+        grp = self._fused_group_for(st)
+        if grp is not None:
+            rtt = self.req_manager.req_to_token_indexs
+            if st.master_plan is not None:
+                mp = st.master_plan
+                n_other = len(mp.peers) - 1
+                res = grp.step(qv.contiguous(), pool_layer, rtt, self.tp_k_head_num_, mp.b_req_idx, mp.b_seq_len, mp.max_len_in_batch,
+                               mp.block_seq, mp.global_mid_o[n_other:], mp.global_mid_lse[n_other:], out=out, out_lse=mp.global_out_lse)
+                return res[0]
+            pp = st.peer_plan
+            grp.step(None, pool_layer, rtt, self.tp_k_head_num_, pp.peer_b_req_idx, pp.peer_b_seq_len, pp.peer_max_len_in_batch,
+                     pp.block_seq, pp.peer_mid_o, pp.peer_mid_lse)
+            return None
         return ringmod.multi_master_decode_attention(qv, pool_layer, self.req_manager.req_to_token_indexs, self.tp_k_head_num_,
                                                      self.sp_comm, self.total_rank_, st.master_plan, st.peer_plan,
                                                      fd.flash_decoding_stage1, fd.flash_decoding_stage2, out=out)
+
+    def _fused_group_for(self, st):
+        """The peer-memory group serving this batch, if one is enabled and the batch has exactly one master whose
+        peers are all instances (the group's layout assumes that)."""
+        if not self._fused_groups:
+            return None
+        if st.master_plan is not None and st.peer_plan is None:
+            master = self.total_rank_
+            if sorted(st.master_plan.peers) != list(range(self.sp_world_size)):
+                return None
+        elif st.peer_plan is not None and st.master_plan is None and len(st.peer_plan.masters) == 1:
+            master = st.peer_plan.masters[0]
+        else:
+            return None
+        return self._fused_groups.get(master)
 
     # ------------------------------------------------------------------------------------------ migration
     @torch.inference_mode()

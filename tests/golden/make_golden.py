@@ -218,7 +218,97 @@ def mem_manager_case():
     print("wrote mem_manager.npz")
 
 
+def _plain(x):
+    if isinstance(x, torch.Tensor):
+        return {"tensor": x.tolist(), "dtype": str(x.dtype).replace("torch.", "")}
+    if isinstance(x, (list, tuple)):
+        return [_plain(y) for y in x]
+    if isinstance(x, (np.integer,)):
+        return int(x)
+    return x
+
+
+def pre_process_case():
+    """Runs the reference's prepare_prefill_inputs / prepare_decode_inputs on CPU: the module is loaded from its
+    source text with the 'cuda' device literals replaced by 'cpu' and its three project imports replaced by small
+    stand-ins for the request record, the batch and the status enum (nothing else changes)."""
+    import json
+    src = open(os.path.join(REF, "loongserve/longserve_server/router/model_infer/pre_process.py")).read()
+    src = src.replace("device='cuda'", "device='cpu'").replace('device="cuda"', 'device="cpu"')
+    src = src.replace("from .infer_batch import requests_mapping, InferReq, InferBatch", "")
+    src = src.replace("from loongserve.longserve_server.io_struct import ReqRunStatus", "")
+    src = src.replace("from loongserve.utils.infer_utils import calculate_time", "")
+    mod = types.ModuleType("ref_pre_process")
+
+    class ReqRunStatus:
+        RUNNING = 1
+
+    class InferReq:
+        def __init__(self, req_idx, prompt_len, cur_kv_len):
+            self.req_idx, self.prompt_len, self.cur_kv_len, self.req_status = req_idx, prompt_len, cur_kv_len, ReqRunStatus.RUNNING
+
+    class InferBatch:
+        def __init__(self, ids):
+            self.request_ids = ids
+
+        def __len__(self):
+            return len(self.request_ids)
+
+    class W:
+        tp_rank, tp_world_size, sp_rank = 0, 1, 0
+
+    mod.__dict__.update(requests_mapping={}, InferReq=InferReq, InferBatch=InferBatch, ReqRunStatus=ReqRunStatus)
+    exec(compile(src, "ref_pre_process", "exec"), mod.__dict__)
+    rm = mod.requests_mapping
+    cases = []
+    rng = np.random.RandomState(11)
+    # ---- prefill: request 'c' was prefilled before (skipped); request 'd' has no token on this instance
+    for need_mig in (False, True):
+        rm.clear()
+        spec = {"a": (5, 0, 7), "b": (2, 0, 1), "c": (9, 33, 4), "d": (0, 0, 0), "e": (7, 0, 12)}      # req_idx, cur_kv_len, local tokens
+        for k, (ri, ckl, n) in spec.items():
+            rm[k] = InferReq(ri, 100, ckl)
+        ids = [rng.randint(0, 32000, size=n).tolist() for (_, _, n) in spec.values()]
+        gk = (ids, 16, [3, 1, 2], 1, [True] * 5, need_mig, [0, 4, 0, 9] if need_mig else None, [10, 4, 3, 40] if need_mig else None)
+        kw, run, not_run = mod.prepare_prefill_inputs(InferBatch(list(spec)), gk, W)
+        cases.append(dict(kind="prefill", requests={k: list(v) for k, v in spec.items()}, input_ids=ids, global_input_kvargs=_plain(list(gk[1:])),
+                          kwargs={k: _plain(v) for k, v in kw.items()}, run=[r.req_idx for r in run], not_run=[r.req_idx for r in not_run]))
+    # ---- prefill with nothing to run
+    rm.clear(); rm["z"] = InferReq(1, 50, 50)
+    kw, run, not_run = mod.prepare_prefill_inputs(InferBatch(["z"]), ([[1, 2]], 8, [0, 1], 0, [True], False, None, None), W)
+    cases.append(dict(kind="prefill", requests={"z": [1, 50, 2]}, input_ids=[[1, 2]], global_input_kvargs=_plain([8, [0, 1], 0, [True], False, None, None]),
+                      kwargs={k: _plain(v) for k, v in kw.items()}, run=[r.req_idx for r in run], not_run=[r.req_idx for r in not_run]))
+    # ---- decode: 4 instances in the order [2, 0, 3, 1], masters = logical ranks 0..1 (or only 0), every logical rank's view
+    for num_masters, sizes in ((2, [2, 4]), (1, [6]), (3, [1, 2, 3])):
+        for lr in range(4):
+            rm.clear()
+            names = ["r%d" % i for i in range(6)]
+            lens = [40, 17, 300, 5, 64, 128]
+            bounds = np.concatenate([[0], np.cumsum(sizes)])
+            lo, hi = (bounds[lr], bounds[lr + 1]) if lr < num_masters else (6, 6)
+            for i, nm in enumerate(names):
+                rm[nm] = InferReq(10 + i, lens[i], lens[i])
+            n_own = int(hi - lo)
+            ids = rng.randint(0, 32000, size=n_own).tolist()
+            first = [lens[i] * 4 + lr for i in range(lo, hi)]
+            gk = (ids, first, num_masters, sizes, [2, 0, 3, 1], lr)
+            kw, run, peer_run, not_run = mod.prepare_decode_inputs(InferBatch(names), gk, W)
+            cases.append(dict(kind="decode", names=names, lens=lens, global_input_kvargs=_plain(list(gk)),
+                              kwargs={k: _plain(v) for k, v in kw.items()}, run=[r.req_idx for r in run],
+                              peer_run=[r.req_idx for r in peer_run], not_run=[r.req_idx for r in not_run],
+                              prompt_len_after=[rm[nm].prompt_len for nm in names]))
+    with open(os.path.join(OUT, "pre_process.json"), "w") as f:
+        json.dump(cases, f, indent=0)
+    print("wrote pre_process.json,", len(cases), "cases")
+
+
 if __name__ == "__main__":
+    only = sys.argv[2:]
+    if only:                         # e.g. `make_golden.py /path/to/reference pre_process`
+        with torch.inference_mode():
+            for name in only:
+                globals()[name + "_case"]()
+        sys.exit(0)
     with torch.inference_mode():
         ring_case("ring_ref_contig_p2.npz", [512], 2, False, 2, 1, 128, 1)
         ring_case("ring_ref_striped_p4.npz", [509, 203], 4, True, 2, 1, 128, 2)
@@ -226,3 +316,4 @@ if __name__ == "__main__":
         torch_att_case()
         kv_cases()
         mem_manager_case()
+        pre_process_case()

@@ -236,10 +236,20 @@ def _runtime_worker(rank, world, port, out):
         peer.peer_b_seq_len = new_len
     dec2 = [rt.token_attention(qd[layer].to(dev) if rank == 0 else None, dstate, layer) for layer in range(L)]
     torch.cuda.synchronize()
+    # ---- the same decode with the exchange done by NVLink stores and flags inside the kernels
+    def gather(b):
+        lst = [None] * world
+        dist.all_gather_object(lst, b)
+        return lst
+    rt.enable_peer_memory_decode(0, gather, max_batch=B)
+    dec3 = [rt.token_attention(qd[layer].to(dev) if rank == 0 else None, dstate, layer) for layer in range(L)]
+    torch.cuda.synchronize()
     torch.save(dict(outs=outs, dec1=[x.cpu() if x is not None else None for x in dec1],
-                    dec2=[x.cpu() if x is not None else None for x in dec2], free=rt.mem_manager.can_use_mem_size,
+                    dec2=[x.cpu() if x is not None else None for x in dec2],
+                    dec3=[x.cpu() if x is not None else None for x in dec3], free=rt.mem_manager.can_use_mem_size,
                     state_sum=int(rt.mem_manager.mem_state.sum()), kept=kept), os.path.join(out, f"rt{rank}.pt"))
     dist.barrier()
+    rt.close()
     comm.close()
     dist.destroy_process_group()
 
@@ -273,7 +283,7 @@ def test_runtime_prefill_keep_decode_migrate_two_gpus(tmp_path):
         # identical before and after the migration
         rd, _ = O.token_decode_attention(qd[layer], kv[layer][:, :Hkv], kv[layer][:, Hkv:], rtab, torch.arange(B, dtype=torch.int32),
                                          torch.tensor(lens, dtype=torch.int32))
-        for key in ("dec1", "dec2"):
+        for key in ("dec1", "dec2", "dec3"):
             got = parts[0][key][layer].float()
             assert bool(((got - rd).abs() <= 2e-2 + 1e-2 * rd.abs()).all()), key
     # slot accounting: kept tokens, then 150 tokens moved from instance 1 to instance 0
@@ -433,27 +443,23 @@ def _forward_kwargs_worker(rank, world, port, out):
     starts = [0, full[0], full[0] + full[1]]
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
     local = [list(range(rank, n, world)) for n in pre]                      # striped placement of the prompt tokens
-    local_ids = torch.cat([ids[s + torch.tensor(l, dtype=torch.long)] for s, l in zip(starts, local)]).to(dev)
+    from loongserve_b200 import pre_process as pp
     b_len = [len(l) for l in local]
     max_tok = max(sum(len(range(r, n, world)) for n in pre) for r in range(world))
-    kwargs = dict(batch_size=B, total_token_num=sum(b_len), max_token_num=max_tok, max_len_in_batch=max(b_len), input_ids=local_ids,
-                  b_req_idx=i32([0, 1, 2]), b_start_loc=i32([0, b_len[0], b_len[0] + b_len[1]]), b_seq_len=i32(b_len),
-                  first_token_global_idx=i32([rank] * B), sp_master_rank=None, logical_sp_peer_ranks=list(range(world)),
-                  logical_sp_rank=rank, newkv_alloc_sp_rank=None, peer_sp_master_rank_list=None, peer_query_buffer_range_list=None,
-                  peer_batch_size=None, peer_max_len_in_batch=None, peer_b_req_idx=None, peer_b_seq_len=None,
-                  need_context_migration=False, kv_cache_index_begin=None, kv_cache_index_end=None, multimodal_params=None, is_prefill=True)
+    reqs = {f"req{b}": pp.InferReq(req_idx=b, prompt_len=pre[b], cur_kv_len=0) for b in range(B)}
+    batch = pp.InferBatch(list(reqs), reqs)
+    worker = pp.Worker(sp_rank=rank, device=dev)
+    local_ids = [ids[s + torch.tensor(l, dtype=torch.long)].tolist() for s, l in zip(starts, local)]
+    kwargs, run, not_run = pp.prepare_prefill_inputs(batch, (local_ids, max_tok, list(range(world)), rank, [True] * B, False, None, None), worker)
+    assert len(run) == B and not not_run
     pre_logits = stack.forward(**kwargs)
-    # decode: instance 0 is the master of all three requests
-    new_ids = torch.stack([ids[s + n - 1] for s, n in zip(starts, full)]).to(dev)
-    if rank == 0:
-        dk = dict(batch_size=B, total_token_num=B, max_token_num=None, max_len_in_batch=max(b_len) + 1, input_ids=new_ids,
-                  b_req_idx=i32([0, 1, 2]), b_start_loc=None, b_seq_len=i32([x + 1 for x in b_len]), first_token_global_idx=i32(pre),
-                  sp_master_rank=0, logical_sp_peer_ranks=list(range(world)), logical_sp_rank=0, is_prefill=False)
-    else:
-        dk = dict(batch_size=0, total_token_num=0, max_token_num=None, max_len_in_batch=0, input_ids=None, b_req_idx=None, b_start_loc=None,
-                  b_seq_len=None, first_token_global_idx=None, sp_master_rank=None, logical_sp_peer_ranks=list(range(world)),
-                  logical_sp_rank=rank, peer_sp_master_rank_list=[0], peer_query_buffer_range_list=[(0, B)], peer_batch_size=B,
-                  peer_max_len_in_batch=max(b_len), peer_b_req_idx=i32([0, 1, 2]), peer_b_seq_len=i32(b_len), is_prefill=False)
+    # decode: instance 0 is the master of all three requests; the router's records hold the tokens cached so far
+    for b in range(B):
+        reqs[f"req{b}"].cur_kv_len = reqs[f"req{b}"].prompt_len = b_len[b]
+    new_ids = [int(ids[s + n - 1]) for s, n in zip(starts, full)]
+    gk = (new_ids if rank == 0 else None, pre if rank == 0 else None, 1, [B], list(range(world)), rank)
+    dk, run, peer_run, _ = pp.prepare_decode_inputs(batch, gk, worker)
+    assert (len(run), len(peer_run)) == ((B, 0) if rank == 0 else (0, B))
     dec_logits = stack.forward(**dk)
     torch.cuda.synchronize()
     torch.save(dict(pre=pre_logits.cpu(), dec=None if dec_logits is None else dec_logits.cpu()), os.path.join(out, f"fw{rank}.pt"))
