@@ -262,6 +262,34 @@ int esp_pool_free_all(esp_pool* pool);
 int esp_pool_state(const esp_pool* pool, int32_t* out_refcounts);
 
 /* ------------------------------------------------------------------------------------------------
+ * Prefill scheduling search (host only, no device work).
+ */
+
+/* Fills the cost table [num_new_req+1, num_instances+1] (caller sets every cell to +inf) and the choice table
+ * [num_new_req+1, num_instances+1, 2] (caller sets every cell to -1) of the batch / instance-run search.
+ * Replaces longserve_c_scheduler.minimize_prefill_iteration_time (longserve_c_scheduler/src/main.cpp:12-87; call site
+ * loongserve/longserve_server/router/manager.py:710-712) with the same argument order: inclusive prefix sums of
+ * the request lengths (longest first), of their squares and of their reciprocals, of the free tokens per instance,
+ * and predictor rows (A, B, C) indexed by ESP degree ([predictor_rows, 3], predictor_rows >= num_instances + 1).
+ * All arrays C-contiguous.  Results are bit-identical to the reference's. */
+int esp_sched_minimize_prefill_iteration_time(int64_t num_new_req, int64_t num_instances, double* min_iteration_times,
+                                              int32_t* min_iteration_times_index, const int64_t* req_input_prefix_sum,
+                                              const int64_t* req_input_square_prefix_sum,
+                                              const double* inverted_req_input_prefix_sum,
+                                              const int64_t* left_token_prefix_sum, const double* predictor_parameters,
+                                              int64_t predictor_rows);
+
+/* The whole planning step of `_schedule_new_req_list` (router/manager.py:687-760) in one call: prefix sums, the
+ * search above, the choice of the instance count with the least cost, and the walk back through the choices.
+ * req_tokens: lengths sorted longest first; left_tokens: free tokens of the instances in the caller's order.
+ * Writes up to num_new_req batches, last batch first (the reference creates them in that order): batch k takes
+ * batch_sizes[k] requests from the end of the not yet assigned requests and batch_instances[k] instances from the end
+ * of the not yet assigned instances.  ESP_ERR_TOO_LARGE when the requests do not fit into the free tokens at all. */
+int esp_sched_plan_prefill(int64_t num_new_req, const int64_t* req_tokens, int64_t num_instances, const int64_t* left_tokens,
+                           const double* predictor_parameters, int64_t predictor_rows, int32_t* batch_sizes,
+                           int32_t* batch_instances, int64_t* num_batches, double* total_cost, double* max_iteration_time);
+
+/* ------------------------------------------------------------------------------------------------
  * Element-wise layer kernels around the attention path (needed only to run a whole Llama layer).
  */
 

@@ -19,7 +19,7 @@ CSRC = os.path.join(HERE, "csrc")
 ROOT = os.path.dirname(HERE)
 
 ATTN_SOURCES = ["kv_scatter.cu", "decode_attention.cu", "prefill_attention.cu", "selftest_umma.cu", "layer_ops.cu",
-                "pool_allocator.cpp"]
+                "pool_allocator.cpp", "prefill_scheduler.cpp"]
 ATTN_LIB = os.path.join(HERE, "libesp_attention.so")
 RNCCL_LIB = os.path.join(HERE, "libesp_rnccl.so")
 
@@ -57,7 +57,8 @@ def build_attention(force: bool = False, verbose_ptxas: bool = False) -> str:
         for s in srcs:
             o = os.path.join(bdir, os.path.basename(s) + ".o")
             if force or _newer(o, deps):
-                _run([_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose_ptxas else []) + ["-c", s, "-o", o])
+                host_only = ["-Xcompiler", "-ffp-contract=off"] if s.endswith(".cpp") else []
+                _run([_nvcc()] + NVCC_FLAGS + host_only + (["-Xptxas", "-v"] if verbose_ptxas else []) + ["-c", s, "-o", o])
             objs.append(o)
         _run([_nvcc(), "-shared", "-cudart", "shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", ATTN_LIB] + objs)
     return ATTN_LIB

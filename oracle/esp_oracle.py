@@ -523,3 +523,33 @@ def llama_layer(x, positions, lens, w, eps, Hq, Hkv, D, act_dtype=None):
     x = r(x + r(r(o).reshape(-1, Hq * D) @ w["o"].float()))
     x = r(x + ffn_block(x, w["ffn_norm"], eps, w["gate_up"], w["down"], act_dtype))
     return x, k, v
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Prefill scheduling search (host logic): restatement of longserve_c_scheduler/src/main.cpp:34-86.
+
+def minimize_prefill_iteration_time(num_new_req, num_instances, best, choice, tok_ps, sq_ps, inv_ps, room_ps, abc):
+    """best [R+1, I+1] float64 (+inf), choice [R+1, I+1, 2] int32 (-1), both filled in place.  Pure-Python loops: small cases
+    only.  Visit order, pruning bounds and the strict comparison follow main.cpp:36-84."""
+    import numpy as _np
+
+    def rng(ps, lo, hi):
+        return ps[hi - 1] - (ps[lo - 1] if lo > 0 else 0)
+
+    best[0, 0] = 0.0
+    for n in range(1, num_new_req + 1):
+        for m in range(1, num_instances + 1):
+            b_hi = int(choice[n, m - 1, 0]) if choice[n, m - 1, 0] != -1 else n          # main.cpp:39-41
+            u_lo = int(choice[n - 1, m, 1]) if choice[n - 1, m, 1] != -1 else 1          # main.cpp:45-47
+            for b in range(1, b_hi + 1):
+                for u in range(m, u_lo - 1, -1):
+                    need = int(rng(tok_ps, n - b, n))
+                    if need > int(rng(room_ps, m - u, m)):                               # main.cpp:61-63
+                        break
+                    need_sq = int(rng(sq_ps, n - b, n))
+                    t = _np.float64(abc[u, 0]) + _np.float64(abc[u, 1]) * _np.float64(need) + _np.float64(abc[u, 2]) * _np.float64(need_sq)
+                    total = t * _np.float64(rng(inv_ps, n - b, n)) + best[n - b, m - u]   # main.cpp:71-76
+                    if total < best[n, m]:
+                        best[n, m] = total
+                        choice[n, m, 0] = b
+                        choice[n, m, 1] = u

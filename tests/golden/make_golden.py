@@ -302,6 +302,44 @@ def pre_process_case():
     print("wrote pre_process.json,", len(cases), "cases")
 
 
+def scheduler_inputs(seed, R, I, tight):
+    """Seeded inputs of the prefill scheduling search, prepared as router/manager.py:691-707 does."""
+    rng = np.random.RandomState(seed)
+    lens = np.sort(np.round(np.exp(rng.uniform(np.log(64), np.log(200000), size=R))).astype(np.int64))[::-1].copy()
+    if tight == "bimodal":                            # a few very long requests and many short ones: plans with several batches
+        lens = np.sort(np.concatenate([rng.randint(100000, 200000, size=max(R // 6, 1)), rng.randint(50, 400, size=R - max(R // 6, 1))]).astype(np.int64))[::-1].copy()
+        tight = False
+    cap = 250000
+    used = np.sort(rng.randint(0, cap // 2 if not tight else cap - 20000, size=I))
+    room = (cap - used).astype(np.int64)
+    if room.sum() < lens.sum():                       # the router only calls the search when everything fits
+        lens = np.maximum(lens * room.sum() // (lens.sum() + 1), 1)
+    abc = np.full((I + 1, 3), np.nan)
+    for u in range(1, I + 1):
+        abc[u] = (0.02 + 0.004 * u, 4.0e-5 / u * (1 + 0.05 * u), 2.5e-10 / u * (1 + 0.03 * u))
+    return lens, room, abc
+
+
+def scheduler_case():
+    """Runs the reference's compiled search (oracle/_ref/longserve_c_scheduler.so, built by oracle/Makefile from the
+    reference's single source file)."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(OUT)), "oracle", "_ref"))
+    import longserve_c_scheduler as ref
+    out = {}
+    shapes = [(1, 1, False), (3, 2, False), (6, 4, False), (12, 8, False), (24, 8, True), (9, 3, True), (40, 8, False), (16, 5, True),
+              (12, 8, "bimodal"), (30, 6, "bimodal"), (7, 4, "bimodal")]
+    for k, (R, I, tight) in enumerate(shapes):
+        lens, room, abc = scheduler_inputs(100 + k, R, I, tight)
+        best = np.full((R + 1, I + 1), np.inf)
+        choice = np.full((R + 1, I + 1, 2), -1, dtype=np.int32)
+        ref.minimize_prefill_iteration_time(R, I, best, choice, np.cumsum(lens), np.cumsum(lens ** 2), np.cumsum(1.0 / lens.astype(np.float64)),
+                                            np.cumsum(room), abc)
+        out[f"c{k}_lens"], out[f"c{k}_room"], out[f"c{k}_abc"], out[f"c{k}_best"], out[f"c{k}_choice"] = lens, room, abc, best, choice
+    out["n"] = np.int64(len(shapes))
+    np.savez_compressed(os.path.join(OUT, "scheduler_dp.npz"), **out)
+    print("wrote scheduler_dp.npz")
+
+
 if __name__ == "__main__":
     only = sys.argv[2:]
     if only:                         # e.g. `make_golden.py /path/to/reference pre_process`
@@ -317,3 +355,4 @@ if __name__ == "__main__":
         kv_cases()
         mem_manager_case()
         pre_process_case()
+        scheduler_case()
