@@ -374,7 +374,7 @@ def e2e_llama(args):
     rt = ESPAttentionRuntime(layers_num=cfg.num_layers, q_head_num=cfg.num_q_heads, kv_head_num=cfg.num_kv_heads,
                              head_dim=cfg.head_dim, max_total_token_num=max_tok + steps + 64, max_req_num=4,
                              max_seq_length=max_tok + steps + 64, sp_world_size=P, total_rank=rank, sp_comm=comm,
-                             dtype=torch.bfloat16, device=dev, decode_block_seq=1024)
+                             dtype=torch.bfloat16, device=dev, decode_block_seq=1024, host_side_allocator=bool(args.e2e_graph))
     stack = LlamaESPStack(cfg, LlamaWeights(cfg, torch.bfloat16, dev, seed=0), rt)
     if args.e2e_exchange == "peer_memory" and world > 1:
         def gather(b):
@@ -419,9 +419,19 @@ def e2e_llama(args):
         dist.barrier()
     local_cnt = Tl
     tok = i32([1])
+    graphed = None
+    if args.e2e_graph and world > 1 and steps > 0:
+        from loongserve_b200.llama_stack import GraphedDecode
+        graphed = GraphedDecode(stack, rt._fused_groups[0], b_req, i32([local_cnt]), positions=i32([T]) if rank == 0 else None,
+                                max_new_tokens=steps).capture()
+        dist.barrier()
     d0.record()
     for s_ in range(steps):
-        if rank == 0:
+        if graphed is not None:
+            lg = graphed.step(tok if rank == 0 else None)
+            if rank == 0:
+                tok = torch.argmax(lg, dim=-1).to(torch.int32)
+        elif rank == 0:
             local_cnt += 1
             dst = rt.prepare_decode(1, 1, local_cnt, b_req, i32([local_cnt]), i32([T + s_]), 0, list(range(P)), 0)
             lg = stack.decode(tok, i32([T + s_]), dst)
@@ -444,7 +454,7 @@ def e2e_llama(args):
         print(json.dumps({
             "metric": "e2e_llama_prefill_tokens_per_s", "value": T / (pre_ms * 1e-3), "unit": "tokens/s", "n_gpus": P,
             "prefill_ms": pre_ms, "decode_ms_per_step": dec_ms, "decode_steps": steps, "higher_is_better": True,
-            "dtype": "bf16", "data": "synthetic", "outputs_finite": bad == 0.0, "decode_exchange": args.e2e_exchange,
+            "dtype": "bf16", "data": "synthetic", "outputs_finite": bad == 0.0, "decode_exchange": args.e2e_exchange, "decode_graph": bool(args.e2e_graph),
             "last_logits_checksum": float(last_logit_sum),
             "prefill_attention_tflops_equiv": attn_flops / (pre_ms * 1e-3) / 1e12,
             "config": {"workload": f"Llama-2-7B architecture ({cfg.num_layers} layers, hidden {cfg.hidden}, {cfg.num_q_heads} heads x {cfg.head_dim}, "
@@ -605,10 +615,14 @@ def main():
     ap.add_argument("--e2e-tokens", type=int, default=524288)
     ap.add_argument("--e2e-decode-steps", type=int, default=128)
     ap.add_argument("--e2e-layers", type=int, default=32)
+    ap.add_argument("--e2e-graph", action="store_true",
+                    help="end-to-end run: replay the decode step as one CUDA graph per instance (implies --e2e-exchange peer_memory)")
     ap.add_argument("--e2e-exchange", default="nccl", choices=["nccl", "peer_memory"],
                     help="decode exchange of the end-to-end run: NCCL messages or NVLink stores + flags in the kernels")
     args = ap.parse_args()
     if args.e2e:
+        if args.e2e_graph:
+            args.e2e_exchange = "peer_memory"
         e2e_llama(args)
         return
     if args.varlen:

@@ -136,6 +136,10 @@ int esp_decode_attention_noalloc(void* o, float* out_lse, const void* q, const v
  * partial straight into the master's partial buffer, a one-word signal publishes it, and the master's merge
  * waits for the peers' flags.  Flags are int32 counters that only grow (one value per step).  Every wait is
  * bounded (about a second) and reports through esp_decode_device_status.
+ * Every flag value is given as `value` plus an optional `value_base`: a device pointer (may be NULL = 0) to an
+ * int32 the kernel adds when it runs.  A caller that records a whole step into a CUDA graph keeps the per-launch
+ * values fixed (1, 2, ... within the step) and advances *value_base by the step's launch count between replays,
+ * on every instance alike, so that replays keep using fresh values.
  */
 
 /* A zero-filled device buffer that other processes on this node can map (CUDA IPC).  esp_peer_buffer_create
@@ -147,13 +151,13 @@ int esp_peer_buffer_close(void* dev_ptr);
 int esp_peer_buffer_destroy(void* dev_ptr);
 
 /* Copy `bytes` (multiple of 16) from src into each of the n_peers (<= 16) destination buffers (peer-mapped
- * pointers, host arrays of device pointers), then store flag_value to each peer's flag with release semantics. */
+ * pointers, host arrays of device pointers), then store flag_value (+ *value_base) to each peer's flag with release semantics. */
 int esp_peer_push(const void* src, void* const* peer_dst, int32_t* const* peer_flags, int32_t n_peers,
-                  int64_t bytes, int32_t flag_value, void* stream);
-/* Publish everything this stream has written so far to the owner of remote_flag: *remote_flag = value. */
-int esp_peer_signal(int32_t* remote_flag, int32_t value, void* stream);
+                  int64_t bytes, int32_t flag_value, const int32_t* value_base, void* stream);
+/* Publish everything this stream has written so far to the owner of remote_flag: *remote_flag = value (+ *value_base). */
+int esp_peer_signal(int32_t* remote_flag, int32_t value, const int32_t* value_base, void* stream);
 
-/* esp_decode_stage1 whose blocks first wait until *wait_flag >= wait_value (q then lives in a buffer the
+/* esp_decode_stage1 whose blocks first wait until *wait_flag >= wait_value + *value_base (q then lives in a buffer the
  * master pushed into) and read q past the L1 cache. */
 int esp_decode_stage1_gated(float* mid_o, float* mid_lse, const void* q, const void* k, const void* v,
                             int64_t k_stride_t, int64_t k_stride_h, int64_t v_stride_t,
@@ -162,12 +166,13 @@ int esp_decode_stage1_gated(float* mid_o, float* mid_lse, const void* q, const v
                             const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
                             int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
                             int32_t seq_block_size, int32_t dtype, float sm_scale,
-                            const int32_t* wait_flag, int32_t wait_value, void* stream);
-/* esp_decode_merge whose blocks first wait until wait_flags[i] >= wait_value for all i < n_wait. */
+                            const int32_t* wait_flag, int32_t wait_value, const int32_t* value_base, void* stream);
+/* esp_decode_merge whose blocks first wait until wait_flags[i] >= wait_value + *value_base for all i < n_wait. */
 int esp_decode_merge_gated(void* o, float* out_lse, const int32_t* b_seqlen, const float* mid_o,
                            const float* mid_lse, int32_t batch, int32_t num_heads, int32_t head_dim,
                            int32_t num_blocks, int32_t block_seq, int32_t o_dtype,
-                           const int32_t* wait_flags, int32_t n_wait, int32_t wait_value, void* stream);
+                           const int32_t* wait_flags, int32_t n_wait, int32_t wait_value, const int32_t* value_base,
+                           void* stream);
 /* Status of the bounded flag waits on the current device, like esp_device_status. */
 int esp_decode_device_status(int32_t out[4], int32_t clear);
 

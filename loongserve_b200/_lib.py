@@ -34,11 +34,11 @@ ATTN_SIGNATURES = {
     "esp_peer_buffer_open": [C.POINTER(C.c_uint8), C.POINTER(_vp)],
     "esp_peer_buffer_close": [_vp],
     "esp_peer_buffer_destroy": [_vp],
-    "esp_peer_push": [_vp, C.POINTER(_vp), C.POINTER(_vp), _i32, _i64, _i32, _vp],
-    "esp_peer_signal": [_vp, _i32, _vp],
+    "esp_peer_push": [_vp, C.POINTER(_vp), C.POINTER(_vp), _i32, _i64, _i32, _vp, _vp],
+    "esp_peer_signal": [_vp, _i32, _vp, _vp],
     "esp_decode_stage1_gated": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _vp,
-                                _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _i32, _vp],
-    "esp_decode_merge_gated": [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _vp],
+                                _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _i32, _vp, _vp],
+    "esp_decode_merge_gated": [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _vp, _vp],
     "esp_decode_device_status": [C.POINTER(_i32), _i32],
     "esp_kv_scatter": [_vp, _i64, _i64, _vp, _i64, _i64, _vp, _i32, _i64, _i32, _i32, _i32, _vp],
     "esp_kv_keep_range": [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp],

@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_stage1_kernel(
     int64_t v_stride_t, int64_t v_stride_h, const int32_t* __restrict__ req_to_tokens,
     int64_t rtt_stride, const int32_t* __restrict__ b_req_idx, const int32_t* __restrict__ b_seqlen,
     int batch, int num_q_heads, int group /* q heads per kv head */, int seq_block_size,
-    float scale_log2, const int32_t* __restrict__ wait_flag, int wait_value) {
+    float scale_log2, const int32_t* __restrict__ wait_flag, int wait_value, const int32_t* __restrict__ value_base) {
     const int blk = blockIdx.x;
     const int hg = blockIdx.y;            // group of G consecutive q heads
     const int b = blockIdx.z;
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_stage1_kernel(
     const bool gated = wait_flag != nullptr;
     if (gated) {
         __shared__ int s_go;
-        if (threadIdx.x == 0) s_go = gate_wait(wait_flag, wait_value, 1) ? 1 : 0;
+        if (threadIdx.x == 0) s_go = gate_wait(wait_flag, wait_value + (value_base ? *value_base : 0), 1) ? 1 : 0;
         __syncthreads();
         if (!s_go) return;
     }
@@ -242,14 +242,16 @@ template <typename OT>
 __global__ void __launch_bounds__(128) decode_merge_kernel(
     OT* __restrict__ o, float* __restrict__ out_lse, const int32_t* __restrict__ b_seqlen,
     const float* __restrict__ mid_o, const float* __restrict__ mid_lse, int batch, int num_heads,
-    int num_blocks, int block_seq, const int32_t* __restrict__ wait_flags, int n_wait, int wait_value) {
+    int num_blocks, int block_seq, const int32_t* __restrict__ wait_flags, int n_wait, int wait_value,
+    const int32_t* __restrict__ value_base) {
     // Gated form: the first n_wait partials are written into this GPU's memory by the peers; each peer raises
     // its flag when its partial is complete.
     if (wait_flags != nullptr) {
         __shared__ int s_go;
         if (threadIdx.x == 0) {
             int okf = 1;
-            for (int i = 0; i < n_wait && okf; ++i) okf = gate_wait(wait_flags + i, wait_value, 2) ? 1 : 0;
+            const int want = wait_value + (value_base ? *value_base : 0);
+            for (int i = 0; i < n_wait && okf; ++i) okf = gate_wait(wait_flags + i, want, 2) ? 1 : 0;
             s_go = okf;
         }
         __syncthreads();
@@ -299,7 +301,8 @@ static int launch_stage1(float* mid_o, float* mid_lse, const void* q, const void
                          int64_t kst, int64_t ksh, int64_t vst, int64_t vsh, const int32_t* rtt,
                          int64_t rtt_stride, const int32_t* b_req_idx, const int32_t* b_seqlen,
                          int batch, int Hq, int Hkv, int max_len, int bs, float scale_log2,
-                         cudaStream_t s, const int32_t* wait_flag = nullptr, int wait_value = 0) {
+                         cudaStream_t s, const int32_t* wait_flag = nullptr, int wait_value = 0,
+                         const int32_t* value_base = nullptr) {
     const int group = Hq / Hkv;
     const int nblk = (max_len + bs - 1) / bs;
     int G = 1;
@@ -307,7 +310,7 @@ static int launch_stage1(float* mid_o, float* mid_lse, const void* q, const void
     dim3 grid(nblk, Hq / G, batch);
 #define ESP_S1(GG) decode_stage1_kernel<T, GG><<<grid, kDecThreads, 0, s>>>(mid_o, mid_lse, (const T*)q, \
         (const T*)k, (const T*)v, kst, ksh, vst, vsh, rtt, rtt_stride, b_req_idx, b_seqlen, batch, Hq, \
-        group, bs, scale_log2, wait_flag, wait_value)
+        group, bs, scale_log2, wait_flag, wait_value, value_base)
     switch (G) {
         case 8: ESP_S1(8); break;
         case 4: ESP_S1(4); break;
@@ -330,7 +333,7 @@ static int decode_stage1_impl(float* mid_o, float* mid_lse, const void* q, const
                                  const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
                                  int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
                                  int32_t seq_block_size, int32_t dtype, float sm_scale, void* stream,
-                                 const int32_t* wait_flag, int32_t wait_value) {
+                                 const int32_t* wait_flag, int32_t wait_value, const int32_t* value_base = nullptr) {
     if (batch == 0 || max_len_in_batch <= 0) return ESP_OK;
     if (!mid_o || !mid_lse || !q || !k || !v || !req_to_tokens || !b_req_idx || !b_seqlen || batch < 0 ||
         num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads || seq_block_size <= 0)
@@ -346,12 +349,12 @@ static int decode_stage1_impl(float* mid_o, float* mid_lse, const void* q, const
         return launch_stage1<__half>(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t,
                                      v_stride_h, req_to_tokens, req_to_tokens_stride, b_req_idx,
                                      b_seqlen, batch, num_q_heads, num_kv_heads, max_len_in_batch,
-                                     seq_block_size, scale, s, wait_flag, wait_value);
+                                     seq_block_size, scale, s, wait_flag, wait_value, value_base);
     if (dtype == ESP_DTYPE_BF16)
         return launch_stage1<__nv_bfloat16>(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t,
                                             v_stride_h, req_to_tokens, req_to_tokens_stride, b_req_idx,
                                             b_seqlen, batch, num_q_heads, num_kv_heads,
-                                            max_len_in_batch, seq_block_size, scale, s, wait_flag, wait_value);
+                                            max_len_in_batch, seq_block_size, scale, s, wait_flag, wait_value, value_base);
     return ESP_ERR_BAD_ARG;
 }
 
@@ -374,18 +377,18 @@ extern "C" int esp_decode_stage1_gated(float* mid_o, float* mid_lse, const void*
                                        const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
                                        int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
                                        int32_t seq_block_size, int32_t dtype, float sm_scale,
-                                       const int32_t* wait_flag, int32_t wait_value, void* stream) {
+                                       const int32_t* wait_flag, int32_t wait_value, const int32_t* value_base, void* stream) {
     if (!wait_flag) return ESP_ERR_BAD_ARG;
     return decode_stage1_impl(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t, v_stride_h, req_to_tokens,
                               req_to_tokens_stride, b_req_idx, b_seqlen, batch, num_q_heads, num_kv_heads, head_dim,
-                              max_len_in_batch, seq_block_size, dtype, sm_scale, stream, wait_flag, wait_value);
+                              max_len_in_batch, seq_block_size, dtype, sm_scale, stream, wait_flag, wait_value, value_base);
 }
 
 static int decode_merge_impl(void* o, float* out_lse, const int32_t* b_seqlen, const float* mid_o,
                                 const float* mid_lse, int32_t batch, int32_t num_heads,
                                 int32_t head_dim, int32_t num_blocks, int32_t block_seq,
                                 int32_t o_dtype, void* stream, const int32_t* wait_flags, int32_t n_wait,
-                                int32_t wait_value) {
+                                int32_t wait_value, const int32_t* value_base = nullptr) {
     if (batch == 0) return ESP_OK;
     if (!o || !out_lse || !b_seqlen || !mid_o || !mid_lse || batch < 0 || num_heads <= 0 ||
         num_blocks < 0 || block_seq <= 0)
@@ -398,16 +401,16 @@ static int decode_merge_impl(void* o, float* out_lse, const int32_t* b_seqlen, c
     switch (o_dtype) {
         case ESP_DTYPE_F32:
             decode_merge_kernel<float><<<grid, 128, 0, s>>>((float*)o, out_lse, b_seqlen, mid_o, mid_lse,
-                                                           batch, num_heads, num_blocks, block_seq, wait_flags, n_wait, wait_value);
+                                                           batch, num_heads, num_blocks, block_seq, wait_flags, n_wait, wait_value, value_base);
             break;
         case ESP_DTYPE_F16:
             decode_merge_kernel<__half><<<grid, 128, 0, s>>>((__half*)o, out_lse, b_seqlen, mid_o,
-                                                            mid_lse, batch, num_heads, num_blocks, block_seq, wait_flags, n_wait, wait_value);
+                                                            mid_lse, batch, num_heads, num_blocks, block_seq, wait_flags, n_wait, wait_value, value_base);
             break;
         case ESP_DTYPE_BF16:
             decode_merge_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>((__nv_bfloat16*)o, out_lse, b_seqlen,
                                                                    mid_o, mid_lse, batch, num_heads,
-                                                                   num_blocks, block_seq, wait_flags, n_wait, wait_value);
+                                                                   num_blocks, block_seq, wait_flags, n_wait, wait_value, value_base);
             break;
         default: return ESP_ERR_BAD_ARG;
     }
@@ -427,10 +430,10 @@ extern "C" int esp_decode_merge_gated(void* o, float* out_lse, const int32_t* b_
                                       const float* mid_lse, int32_t batch, int32_t num_heads,
                                       int32_t head_dim, int32_t num_blocks, int32_t block_seq,
                                       int32_t o_dtype, const int32_t* wait_flags, int32_t n_wait,
-                                      int32_t wait_value, void* stream) {
+                                      int32_t wait_value, const int32_t* value_base, void* stream) {
     if (n_wait < 0 || (n_wait > 0 && !wait_flags)) return ESP_ERR_BAD_ARG;
     return decode_merge_impl(o, out_lse, b_seqlen, mid_o, mid_lse, batch, num_heads, head_dim, num_blocks, block_seq,
-                             o_dtype, stream, n_wait > 0 ? wait_flags : nullptr, n_wait, wait_value);
+                             o_dtype, stream, n_wait > 0 ? wait_flags : nullptr, n_wait, wait_value, value_base);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -441,16 +444,17 @@ constexpr int kMaxPushPeers = 16;
 struct PushTargets { void* dst[kMaxPushPeers]; int32_t* flag[kMaxPushPeers]; };
 
 // grid = number of peers; one CTA copies `bytes` (multiple of 16) into one peer and then publishes the flag
-__global__ void __launch_bounds__(1024) peer_push_kernel(const uint4* __restrict__ src, PushTargets tg, int64_t nvec, int value) {
+__global__ void __launch_bounds__(1024) peer_push_kernel(const uint4* __restrict__ src, PushTargets tg, int64_t nvec, int value,
+                                                         const int32_t* __restrict__ value_base) {
     uint4* dst = reinterpret_cast<uint4*>(tg.dst[blockIdx.x]);
     for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) dst[i] = src[i];
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0) st_release_sys(tg.flag[blockIdx.x], value);
+    if (threadIdx.x == 0) st_release_sys(tg.flag[blockIdx.x], value + (value_base ? *value_base : 0));
 }
-__global__ void peer_signal_kernel(int32_t* flag, int value) {
+__global__ void peer_signal_kernel(int32_t* flag, int value, const int32_t* __restrict__ value_base) {
     __threadfence_system();
-    st_release_sys(flag, value);
+    st_release_sys(flag, value + (value_base ? *value_base : 0));
 }
 }  // namespace esp
 
@@ -489,7 +493,7 @@ extern "C" int esp_peer_buffer_destroy(void* dev_ptr) {
 }
 
 extern "C" int esp_peer_push(const void* src, void* const* peer_dst, int32_t* const* peer_flags, int32_t n_peers,
-                             int64_t bytes, int32_t flag_value, void* stream) {
+                             int64_t bytes, int32_t flag_value, const int32_t* value_base, void* stream) {
     if (n_peers == 0) return ESP_OK;
     if (!src || !peer_dst || !peer_flags || n_peers < 0 || bytes < 0) return ESP_ERR_BAD_ARG;
     if (n_peers > kMaxPushPeers) return ESP_ERR_TOO_LARGE;
@@ -499,14 +503,14 @@ extern "C" int esp_peer_push(const void* src, void* const* peer_dst, int32_t* co
         if (!peer_dst[i] || !peer_flags[i] || !aligned16(peer_dst[i])) return ESP_ERR_BAD_ARG;
         tg.dst[i] = peer_dst[i]; tg.flag[i] = peer_flags[i];
     }
-    peer_push_kernel<<<n_peers, 1024, 0, (cudaStream_t)stream>>>((const uint4*)src, tg, bytes / 16, flag_value);
+    peer_push_kernel<<<n_peers, 1024, 0, (cudaStream_t)stream>>>((const uint4*)src, tg, bytes / 16, flag_value, value_base);
     ESP_LAUNCH_CHECK("peer_push_kernel");
     return ESP_OK;
 }
 
-extern "C" int esp_peer_signal(int32_t* remote_flag, int32_t value, void* stream) {
+extern "C" int esp_peer_signal(int32_t* remote_flag, int32_t value, const int32_t* value_base, void* stream) {
     if (!remote_flag) return ESP_ERR_BAD_ARG;
-    peer_signal_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(remote_flag, value);
+    peer_signal_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(remote_flag, value, value_base);
     ESP_LAUNCH_CHECK("peer_signal_kernel");
     return ESP_OK;
 }

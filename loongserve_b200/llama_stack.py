@@ -151,3 +151,120 @@ class LlamaESPStack:
     def _logits(self, x):
         h = layer_ops.rms_norm(x.contiguous(), self.w.final_norm, self.cfg.rms_eps)
         return torch.mm(h, self.w.lm_head).float()
+
+
+class GraphedDecode:
+    """One decode iteration of an ESP group (all layers, the attention exchange over peer memory, logits) recorded
+    once per instance into a CUDA graph and replayed every step, so that a step costs one graph launch instead of
+    a few hundred kernel launches issued from Python.  The reference issues every kernel of every layer from Python
+    (longserve_transformer_layer_infer.py:372-456) and allocates its per-step buffers anew (longserve_model.py:438-538).
+
+    Everything that changes from step to step lives in fixed device buffers the graph reads: the new token ids, the
+    pool slots of the new tokens, the requests' local lengths and positions (advanced inside the graph), and the base
+    of the exchange's flag values (``FusedDecodeGroup.step(step_value=, value_base=)``), advanced by one per layer
+    inside the graph.  Grid sizes are recorded for ``max_new_tokens`` more tokens than the longest request has now;
+    sequence blocks beyond a request's current length return at once.
+
+    Single master per group (instance ``group.master``); every instance of the group builds one of these, calls
+    ``capture()`` once and then ``step()`` the same number of times.
+    """
+
+    def __init__(self, stack: LlamaESPStack, group, b_req_idx: torch.Tensor, b_seq_len: torch.Tensor,
+                 positions: Optional[torch.Tensor] = None, max_new_tokens: int = 128, block_seq: Optional[int] = None):
+        """``b_req_idx`` / ``b_seq_len``: the master's requests as stored on THIS instance (int32; on the master the
+        lengths exclude the token the first step adds).  ``positions`` (master only): global position of the first new
+        token of every request."""
+        self.stack, self.group = stack, group
+        rt, cfg = stack.rt, stack.cfg
+        self.is_master = group.rank == group.master
+        dev = b_seq_len.device
+        B = b_seq_len.shape[0]
+        self.B = B
+        longest = int(b_seq_len.max())                                   # set-up time read-back
+        self.bound = longest + (int(max_new_tokens) if self.is_master else 0)
+        self.block_seq = int(block_seq or rt.decode_block_seq or 256)
+        nblk = (self.bound + self.block_seq - 1) // self.block_seq
+        f32 = dict(dtype=torch.float32, device=dev)
+        Hq, Hkv, D = cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim
+        self.b_req_idx = b_req_idx.to(torch.int32).contiguous().clone()
+        self.seq_len = b_seq_len.to(torch.int32).contiguous().clone()
+        self.mid_o = torch.empty((nblk, B, Hq, D), **f32)
+        self.mid_lse = torch.empty((nblk, B, Hq), **f32)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._synced = None
+        if self.is_master:
+            assert positions is not None and positions.shape[0] == B
+            self.pos = positions.to(torch.int64).contiguous().clone()
+            self.input_ids = torch.zeros(B, dtype=torch.int64, device=dev)
+            self.new_slots = torch.zeros(B, dtype=torch.int64, device=dev)
+            self.kv_scratch = torch.empty((B, 2 * Hkv, D), dtype=rt.dtype, device=dev)
+            self.out_lse = torch.empty((B, Hq), **f32)
+            self.logits = torch.empty((B, cfg.vocab), **f32)
+        self.graph = None
+        self.steps_left = int(max_new_tokens)
+
+    @torch.inference_mode()
+    def _record(self):
+        stack, rt, cfg, grp = self.stack, self.stack.rt, self.stack.cfg, self.group
+        Hq, Hkv, D, B = cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim, self.B
+        rtt = rt.req_manager.req_to_token_indexs
+        L = cfg.num_layers
+        if not self.is_master:
+            for li in range(L):
+                grp.step(None, rt.mem_manager.kv_buffer[li], rtt, Hkv, self.b_req_idx, self.seq_len, self.bound, self.block_seq,
+                         self.mid_o, self.mid_lse, step_value=li + 1, value_base=self.counter)
+            self.counter.add_(L)
+            return
+        from . import kv_ops
+        self.seq_len.add_(1)                                             # lengths now include the new token
+        kv_ops.copy_kv_index_to_req(rtt, self.b_req_idx, self.seq_len, self.new_slots)
+        x = stack.w.embed[self.input_ids]
+        cos, sin = rope_cos_sin(self.pos, D, cfg.rope_base, x.dtype)
+        for li, lw in enumerate(stack.w.layers):
+            pool = rt.mem_manager.kv_buffer[li]
+            h = layer_ops.rms_norm(x, lw["att_norm"], cfg.rms_eps)
+            q = torch.mm(h, lw["q"])
+            torch.mm(h, lw["kv"], out=self.kv_scratch.view(B, 2 * Hkv * D))
+            layer_ops.rotary_emb(q.view(B, Hq, D), self.kv_scratch[:, :Hkv, :], cos, sin)
+            kv_ops.destindex_copy_kv(self.kv_scratch, self.new_slots, pool)
+            o, _ = grp.step(q.view(B, Hq, D), pool, rtt, Hkv, self.b_req_idx, self.seq_len, self.bound, self.block_seq,
+                            self.mid_o, self.mid_lse, out_lse=self.out_lse, step_value=li + 1, value_base=self.counter)
+            x.add_(torch.mm(o.view(B, Hq * D), lw["o"]))
+            x.add_(layer_ops.ffn_block(x, lw["ffn_norm"], cfg.rms_eps, lw["gate_up"], lw["down"]))
+        self.logits.copy_(stack._logits(x))
+        self.pos.add_(1)
+        self.counter.add_(L)
+
+    def capture(self):
+        """Record the step.  Nothing runs on the GPU here; run at least one ordinary decode step on this process
+        first so that library workspaces exist."""
+        grp = self.group
+        if self.is_master and (grp._ones is None or grp._ones.shape[0] != self.B):
+            # the merge over the P partial slots reads this constant; it must hold its value before the first replay
+            grp._ones = torch.full((self.B,), grp.world, dtype=torch.int32, device=self.seq_len.device)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._record()
+        return self
+
+    @torch.inference_mode()
+    def step(self, input_ids: Optional[torch.Tensor] = None, new_slots: Optional[torch.Tensor] = None):
+        """Replay one step.  Master: ``input_ids`` [B] (device or host) are the tokens to feed, ``new_slots`` [B] the
+        pool slots their K/V rows go to (default: allocated from the runtime's pool manager); returns the logits
+        buffer [B, vocab] (overwritten by the next step).  Peers pass nothing and get None."""
+        assert self.graph is not None, "call capture() first"
+        assert self.steps_left > 0, "the graph was recorded for max_new_tokens steps"
+        grp, L = self.group, self.stack.cfg.num_layers
+        if self._synced != grp.step_id:                                  # steps ran outside the graph since the last replay
+            self.counter.fill_(grp.step_id)
+        if self.is_master:
+            if new_slots is None:
+                new_slots = self.stack.rt.mem_manager.alloc(self.B)
+            self.new_slots.copy_(new_slots, non_blocking=True)
+            self.input_ids.copy_(input_ids, non_blocking=True)
+        self.graph.replay()
+        grp.advance(L)
+        self._synced = grp.step_id
+        self.steps_left -= 1
+        return self.logits if self.is_master else None

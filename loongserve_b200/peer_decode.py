@@ -65,15 +65,23 @@ class FusedDecodeGroup:
 
     @torch.inference_mode()
     def step(self, q, pool_layer, req_to_token_indexs, num_kv_heads: int, b_req_idx, b_seq_len, max_len_in_batch: int,
-             block_seq: int, mid_o, mid_lse, out=None, out_lse=None):
+             block_seq: int, mid_o, mid_lse, out=None, out_lse=None, step_value: Optional[int] = None, value_base=None):
         """One layer's decode attention.  On the master ``q`` is [batch, Hq, D] and the result (o in q's dtype, lse)
         is returned; on a peer ``q`` is None, (b_req_idx, b_seq_len) describe the master's requests as stored here,
         and None is returned.  mid_o / mid_lse: local scratch [nblk, batch, Hq, D] / [nblk, batch, Hq] fp32
         (on the master the first world-1 blocks of the merge come from the peers, so scratch only needs the local
-        blocks)."""
+        blocks).
+
+        ``step_value`` / ``value_base`` are for callers that record steps into a CUDA graph: the flag value of this
+        call becomes ``step_value + value_base[0]`` (an int32 device tensor read when the kernels run) instead of the
+        group's own host-side counter; see ``advance``."""
         lib, s = self._lib, stream_ptr()
-        self.step_id += 1
-        sid = self.step_id
+        if step_value is None:
+            self.step_id += 1
+            sid, vb = self.step_id, None
+        else:
+            assert value_base is not None and value_base.dtype == torch.int32
+            sid, vb = int(step_value), ptr(value_base)
         batch = b_seq_len.shape[0]
         assert 0 < batch <= self.B, "batch exceeds the max_batch the shared region was sized for"
         Hq, D, Hkv = self.Hq, self.D, num_kv_heads
@@ -86,7 +94,7 @@ class FusedDecodeGroup:
             if n:
                 dsts = (C.c_void_p * n)(*[self.peer_base[r] for r in self.peers])
                 flags = (C.c_void_p * n)(*[self.peer_base[r] + self.off_flags for r in self.peers])
-                _lib.check(lib.esp_peer_push(ptr(q), dsts, flags, n, batch * Hq * D * 2, sid, s), "esp_peer_push")
+                _lib.check(lib.esp_peer_push(ptr(q), dsts, flags, n, batch * Hq * D * 2, sid, vb, s), "esp_peer_push")
             _lib.check(lib.esp_decode_stage1(ptr(mid_o), ptr(mid_lse), ptr(q), ptr(k_cache), ptr(v_cache), k_cache.stride(0),
                                              k_cache.stride(1), v_cache.stride(0), v_cache.stride(1), ptr(req_to_token_indexs),
                                              req_to_token_indexs.stride(0), ptr(b_req_idx), ptr(b_seq_len), batch, Hq, Hkv, D,
@@ -103,14 +111,14 @@ class FusedDecodeGroup:
             # the P slots are laid out [P, batch, Hq, D] for this step's batch: a merge over P one-token "blocks"
             _lib.check(lib.esp_decode_merge_gated(ptr(o), ptr(lse), ptr(self._ones), self.base + self.off_o,
                                                   self.base + self.off_lse, batch, Hq, D, self.world, 1, dtype_tag(o),
-                                                  self.base + self.off_flags + 4, n, sid, s), "esp_decode_merge_gated")
+                                                  self.base + self.off_flags + 4, n, sid, vb, s), "esp_decode_merge_gated")
             return o, lse
         # ---- peer
         qbuf = self.base
         _lib.check(lib.esp_decode_stage1_gated(ptr(mid_o), ptr(mid_lse), qbuf, ptr(k_cache), ptr(v_cache), k_cache.stride(0),
                                                k_cache.stride(1), v_cache.stride(0), v_cache.stride(1), ptr(req_to_token_indexs),
                                                req_to_token_indexs.stride(0), ptr(b_req_idx), ptr(b_seq_len), batch, Hq, Hkv, D,
-                                               max_len_in_batch, block_seq, tag, 0.0, self.base + self.off_flags, sid, s),
+                                               max_len_in_batch, block_seq, tag, 0.0, self.base + self.off_flags, sid, vb, s),
                    "esp_decode_stage1_gated")
         mbase = self.peer_base[self.master]
         slot = self.rank
@@ -118,8 +126,13 @@ class FusedDecodeGroup:
                                         ptr(b_seq_len), ptr(mid_o), ptr(mid_lse), batch, Hq, D, nblk, block_seq,
                                         _lib.ESP_DTYPE_F32, s), "esp_decode_merge (remote)")
         flag_idx = 1 + self.peers.index(self.rank)
-        _lib.check(lib.esp_peer_signal(mbase + self.off_flags + 4 * flag_idx, sid, s), "esp_peer_signal")
+        _lib.check(lib.esp_peer_signal(mbase + self.off_flags + 4 * flag_idx, sid, vb, s), "esp_peer_signal")
         return None
+
+    def advance(self, n_steps: int):
+        """Tell the group that ``n_steps`` steps ran outside its own counting (a graph replay), so that later calls
+        without ``step_value`` keep using values above everything already stored in the flags."""
+        self.step_id += int(n_steps)
 
     def device_status(self, clear: bool = True):
         """(code, block, which wait, value) of the bounded flag waits on this device; code 0 = none expired."""

@@ -489,3 +489,90 @@ def test_forward_with_reference_kwargs_two_gpus(tmp_path):
     dec = torch.load(os.path.join(str(tmp_path), "fw0.pt"))["dec"]
     err = (dec - ref).abs()
     assert bool((err <= 5e-2 + 5e-2 * ref.abs()).all()), err.max()
+
+
+def _graphed_decode_worker(rank, world, port, out):
+    """The same prompt and the same fed tokens through two runtimes: decode steps issued kernel by kernel, and the
+    step replayed as one CUDA graph per instance.  Both use the peer-memory exchange."""
+    dist, comm = _setup(rank, world, port)
+    from loongserve_b200.attention_runtime import ESPAttentionRuntime
+    from loongserve_b200.llama_stack import GraphedDecode, LlamaConfig, LlamaESPStack, LlamaWeights
+    dev = torch.device("cuda", rank)
+    cfg = LlamaConfig(num_layers=3, hidden=512, num_q_heads=4, num_kv_heads=2, head_dim=128, ffn=1024, vocab=1000)
+    weights = LlamaWeights(cfg, torch.bfloat16, dev, seed=4)
+
+    def gather(b):
+        lst = [None] * world
+        dist.all_gather_object(lst, b)
+        return lst
+
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    lens = [700, 45]
+    B, n_steps = len(lens), 4
+    g = torch.Generator().manual_seed(21)
+    ids = torch.randint(0, cfg.vocab, (sum(lens),), generator=g)
+    fed = torch.randint(0, cfg.vocab, (n_steps, B), generator=g)
+    starts = [0, lens[0]]
+    local = [list(range(rank, n, world)) for n in lens]
+    b_len = [len(l) for l in local]
+    local_ids = torch.cat([ids[s + torch.tensor(l, dtype=torch.long)] for s, l in zip(starts, local)]).to(dev)
+    pos = torch.cat([torch.tensor(l, dtype=torch.long) for l in local]).to(dev)
+    max_tok = max(sum(len(range(r, n, world)) for n in lens) for r in range(world))
+    results = {}
+    for mode in ("eager", "graph"):
+        rt = ESPAttentionRuntime(layers_num=cfg.num_layers, q_head_num=4, kv_head_num=2, head_dim=128, max_total_token_num=2048,
+                                 max_req_num=8, max_seq_length=2048, sp_world_size=world, total_rank=rank, sp_comm=comm,
+                                 dtype=torch.bfloat16, device=dev, decode_block_seq=256, host_side_allocator=True)
+        rt.enable_peer_memory_decode(0, gather, max_batch=B)
+        stack = LlamaESPStack(cfg, weights, rt)
+        st = rt.prepare_prefill(B, sum(b_len), max_tok, max(b_len), i32([0, 1]), i32([0, b_len[0]]), i32(b_len), i32([rank] * B),
+                                list(range(world)), rank, request_lengths=lens, striped=True)
+        stack.prefill(local_ids, pos, st)
+        logits = []
+        cnt = list(b_len)
+        if mode == "eager":
+            for s_ in range(n_steps):
+                if rank == 0:
+                    cnt = [c + 1 for c in cnt]
+                    d = rt.prepare_decode(B, B, max(cnt), i32([0, 1]), i32(cnt), i32([n + s_ for n in lens]), 0, list(range(world)), 0)
+                    logits.append(stack.decode(fed[s_].to(dev), i32([n + s_ for n in lens]), d).cpu())
+                else:
+                    d = rt.prepare_decode(0, 0, 0, None, None, None, None, list(range(world)), rank, peer_sp_master_rank_list=[0],
+                                          peer_query_buffer_range_list=[(0, B)], peer_batch_size=B, peer_max_len_in_batch=max(cnt),
+                                          peer_b_req_idx=i32([0, 1]), peer_b_seq_len=i32(cnt))
+                    stack.decode(None, None, d)
+        else:
+            gd = GraphedDecode(stack, rt._fused_groups[0], i32([0, 1]), i32(cnt), positions=i32(lens) if rank == 0 else None,
+                               max_new_tokens=n_steps).capture()
+            dist.barrier()
+            for s_ in range(n_steps):
+                lg = gd.step(fed[s_] if rank == 0 else None)
+                if rank == 0:
+                    logits.append(lg.cpu().clone())
+        torch.cuda.synchronize()
+        status = rt._fused_groups[0].device_status()
+        results[mode] = dict(logits=logits, status=status, table=rt.req_manager.req_to_token_indexs[:2, :b_len[0] + n_steps].cpu(),
+                             free=rt.mem_manager.can_use_mem_size)
+        dist.barrier()
+        rt.close()
+    torch.save(results, os.path.join(out, f"gd{rank}.pt"))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+
+
+def test_graphed_decode_matches_kernel_by_kernel_decode_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    mp.spawn(_graphed_decode_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        res = torch.load(os.path.join(str(tmp_path), f"gd{r}.pt"))
+        assert res["eager"]["status"][0] == 0 and res["graph"]["status"][0] == 0        # no flag wait ran out
+        assert torch.equal(res["eager"]["table"], res["graph"]["table"])                # same slots registered
+        assert res["eager"]["free"] == res["graph"]["free"]
+        if r == 0:
+            assert len(res["graph"]["logits"]) == 4
+            for a, b in zip(res["eager"]["logits"], res["graph"]["logits"]):
+                assert bool(torch.isfinite(b).all())
+                assert bool(((a - b).abs() <= 1e-3 + 1e-3 * a.abs()).all()), (a - b).abs().max()
