@@ -33,7 +33,8 @@ extern "C" {
 const char* esp_strerror(int code);
 /* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
 const char* esp_last_cuda_error(void);
-/* ABI version of this header (bumped on incompatible change). */
+/* ABI version of this header (bumped on incompatible change).  Version 2: the peer-memory entry points take `value_base`. */
+#define ESP_ABI_VERSION 2
 int esp_abi_version(void);
 
 /* ------------------------------------------------------------------------------------------------

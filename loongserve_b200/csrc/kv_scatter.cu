@@ -206,7 +206,7 @@ extern "C" const char* esp_strerror(int code) {
 }
 
 extern "C" const char* esp_last_cuda_error(void) { return last_cuda_error_buf(); }
-extern "C" int esp_abi_version(void) { return 2; }
+extern "C" int esp_abi_version(void) { return ESP_ABI_VERSION; }
 
 extern "C" int esp_kv_scatter(const void* src, int64_t src_row_stride, int64_t src_head_stride,
                               void* out, int64_t out_row_stride, int64_t out_head_stride,

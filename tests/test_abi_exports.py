@@ -67,3 +67,16 @@ def test_ops_refuse_cpu_tensors(built):
     from loongserve_b200 import kv_ops
     with pytest.raises(RuntimeError, match="CUDA"):
         kv_ops.destindex_copy_kv(torch.zeros(2, 2, 8), torch.zeros(2, dtype=torch.int32), torch.zeros(4, 2, 8))
+
+
+def test_abi_version_matches_header_and_python_table(built):
+    src = open(os.path.join(ROOT, "include", "esp_attention.h")).read()
+    header_version = int(re.search(r"#define\s+ESP_ABI_VERSION\s+(\d+)", src).group(1))
+    lib = C.CDLL(built.ATTN_LIB)
+    lib.esp_abi_version.restype = C.c_int
+    assert lib.esp_abi_version() == header_version == built.ESP_ABI_VERSION
+
+
+def test_build_entry_point_runs():
+    import __graft_entry__ as g
+    g.build()
