@@ -116,6 +116,24 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
+def use_all_host_cores(torch) -> int:
+    """The CPU arm uses every physical core this process may run on.  torch.distributed.run exports OMP_NUM_THREADS=1
+    to its workers, which would otherwise leave the CPU arm on a single thread."""
+    try:
+        allowed = len(os.sched_getaffinity(0))
+    except AttributeError:
+        allowed = os.cpu_count() or 1
+    try:
+        import psutil
+        physical = psutil.cpu_count(logical=False) or allowed
+    except Exception:
+        physical = allowed
+    n = max(1, min(allowed, physical))
+    if torch.get_num_threads() < n:
+        torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
 def run_reference_arm(args):
     """The reference path's CPU implementation (the oracle restatement) on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -123,7 +141,7 @@ def run_reference_arm(args):
         return
     import torch
     from oracle import esp_oracle as O
-    cores = torch.get_num_threads()
+    cores = use_all_host_cores(torch)
     Ts = int(os.environ.get("ESP_BENCH_CPU_TOKENS", "8192"))
     g = torch.Generator().manual_seed(0)
     q = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
@@ -578,6 +596,7 @@ def ops_bench(args):
 
 def cpu_baseline(torch):
     from oracle import esp_oracle as O
+    use_all_host_cores(torch)
     Ts = int(os.environ.get("ESP_BENCH_CPU_TOKENS", "8192"))
     g = torch.Generator().manual_seed(0)
     q = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
