@@ -71,3 +71,32 @@ def test_uninstall_restores_the_module_table():
     assert "longserve_cuda_kernels" not in sys.modules and "rnccl" not in sys.modules
     with pytest.raises(ImportError):
         importlib.import_module("longserve_cuda_kernels")
+
+
+def test_unmodified_reference_modules_import_against_this_package():
+    """With the reference checkout at hand (build container only), its layer-infer and model modules import unchanged
+    and bind this package's kernels.  The checkout must be importable BEFORE install() so that its real parent packages
+    are used."""
+    import os
+    ref = os.environ.get("ESP_REFERENCE_DIR", "/root/reference")
+    if not os.path.isdir(os.path.join(ref, "loongserve", "models", "llama")):
+        pytest.skip("reference checkout not present")
+    before = set(sys.modules)
+    sys.path.insert(0, ref)
+    try:
+        dropin.install()
+        li = importlib.import_module("loongserve.models.llama.layer_infer.longserve_transformer_layer_infer")
+        lm = importlib.import_module("loongserve.models.llama.longserve_model")
+        assert hasattr(li, "LongServeTransformerLayerInfer") and hasattr(lm, "LongServeLlamaModel")
+        assert li.context_attention_fwd.__module__ == "loongserve_b200.context_attention"
+        assert li.rnccl.RNCCLComm.__module__ == "loongserve_b200.rnccl"
+        assert li.longserve_cuda_kernels.flash_decoding_stage1.__module__ == "loongserve_b200.flash_decoding"
+        assert li.pre_copy_and_register_kv.__module__ == "loongserve_b200.kv_ops"
+        assert lm.LongServeMemoryManager.__module__ == "loongserve_b200.mem_manager"
+        assert lm.init_req_to_token_indexes.__module__ == "loongserve_b200.kv_ops"
+    finally:
+        dropin.uninstall()
+        sys.path.remove(ref)
+        for name in set(sys.modules) - before:
+            if name.split(".")[0] in ("loongserve", "rnccl", "longserve_cuda_kernels", "longserve_c_scheduler"):
+                sys.modules.pop(name, None)
