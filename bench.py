@@ -634,6 +634,8 @@ def main():
     ap.add_argument("--e2e-tokens", type=int, default=524288)
     ap.add_argument("--e2e-decode-steps", type=int, default=128)
     ap.add_argument("--e2e-layers", type=int, default=32)
+    ap.add_argument("--e2e-head-chunks", type=int, default=0,
+                    help="head chunks of the pipelined host-buffer leg (default 4 up to 2 GPUs, else 2)")
     ap.add_argument("--e2e-graph", action="store_true",
                     help="end-to-end run: replay the decode step as one CUDA graph per instance (implies --e2e-exchange peer_memory)")
     ap.add_argument("--e2e-exchange", default="nccl", choices=["nccl", "peer_memory"],
@@ -744,11 +746,19 @@ def main():
         hkv = torch.empty(kv_local.shape, dtype=q.dtype).pin_memory(); hkv.copy_(kv_local)
         ho = torch.empty(o.shape, dtype=o.dtype).pin_memory()
 
+        # the public host-buffer call: chunks of heads pipelined over the copy engines and the ring
+        from loongserve_b200.host_pipeline import HostPrefillPipeline
+        chunks = args.e2e_head_chunks or (4 if P <= 2 else 2)
+        o_sample = o[:512].clone()                   # rows of the device-resident run, to check the host-buffer result against
+        del o, m, l
+        recv.clear()
+        del q, kv_local
+        torch.cuda.empty_cache()
+        pipe = HostPrefillPipeline(Tl, max_tok, H, H, D, rank=rank, peers=list(range(P)), metas=metas, stride=stride,
+                                   max_len_in_batch=Tl, comm=comm, head_chunks=chunks, device=dev, overlap=not args.no_overlap)
+
         def e2e_step():
-            q.copy_(hq, non_blocking=True)
-            kv_local.copy_(hkv, non_blocking=True)
-            step()
-            ho.copy_(o, non_blocking=True)
+            pipe.run(hq, hkv, ho)
 
         e2e_step(); torch.cuda.synchronize()
         if world > 1:
@@ -766,12 +776,14 @@ def main():
             ems = float(tms.item())
         e2e = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": (hq.numel() + hkv.numel()) * 2 * P, "d2h_bytes_per_step": ho.numel() * 2 * P,
-               "ms_per_step": ems, "steps": n_e2e}
-        del hq, hkv, ho
+               "ms_per_step": ems, "steps": n_e2e, "head_chunks": chunks,
+               "matches_device_run": bool(torch.equal(ho[:512].view(torch.int16), o_sample.cpu().view(torch.int16))),
+               "api": "loongserve_b200.host_pipeline.HostPrefillPipeline.run(pinned q, kv, o)"}
+        del hq, hkv, ho, pipe
+        torch.cuda.empty_cache()
 
     decode_dist = decode_fused = None
     if not args.skip_extras and P > 1:
-        del q, kv_local, o, recv
         torch.cuda.empty_cache()
         decode_dist = decode_bench_dist(torch, dist, comm, peaks, rank, P)
         decode_fused = decode_bench_dist(torch, dist, comm, peaks, rank, P, fused=True)
@@ -801,7 +813,6 @@ def main():
             out["decode"] = decode_dist
             out["decode_peer_memory"] = decode_fused
         if not args.skip_extras and P == 1:
-            del q, kv_local, o
             torch.cuda.empty_cache()
             out["decode"] = decode_bench(torch, peaks)
             out["scatter"] = scatter_bench(torch, peaks)

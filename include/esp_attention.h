@@ -267,6 +267,13 @@ int esp_pool_decrease_refs(esp_pool* pool, const int64_t* ids, int64_t n);
 int esp_pool_free_all(esp_pool* pool);
 int esp_pool_state(const esp_pool* pool, int32_t* out_refcounts);
 
+/* Strided copy between pinned host memory and device memory (or device to device) on `stream`: `height` rows of
+ * `width` bytes, row starts `spitch` / `dpitch` bytes apart.  kind: 0 host->device, 1 device->host, 2 device->device.
+ * Used to move a chunk of heads of a [tokens, heads, D] host tensor without touching the other heads; the reference keeps
+ * every tensor on the device and has no counterpart. */
+int esp_memcpy_2d(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width, int64_t height,
+                  int32_t kind, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Prefill scheduling search (host only, no device work).
  */

@@ -60,6 +60,7 @@ ATTN_SIGNATURES = {
     "esp_pool_decrease_refs": [_vp, _vp, _i64],
     "esp_pool_free_all": [_vp],
     "esp_pool_state": [_vp, _vp],
+    "esp_memcpy_2d": [_vp, _i64, _vp, _i64, _i64, _i64, _i32, _vp],
     "esp_sched_minimize_prefill_iteration_time": [_i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64],
     "esp_sched_plan_prefill": [_i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp],
     "esp_rms_norm": [_vp, _vp, _vp, _i64, _i32, _f32, _i32, _vp],

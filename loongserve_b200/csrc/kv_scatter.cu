@@ -380,3 +380,12 @@ extern "C" int esp_mig_scatter(const void* recv_buf, int64_t total_tokens, int32
     ESP_LAUNCH_CHECK("mig_scatter_kernel");
     return ESP_OK;
 }
+
+extern "C" int esp_memcpy_2d(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width, int64_t height,
+                             int32_t kind, void* stream) {
+    if (width == 0 || height == 0) return ESP_OK;
+    if (!dst || !src || width < 0 || height < 0 || dpitch < width || spitch < width || kind < 0 || kind > 2) return ESP_ERR_BAD_ARG;
+    const cudaMemcpyKind k = kind == 0 ? cudaMemcpyHostToDevice : kind == 1 ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+    ESP_CUDA_TRY(cudaMemcpy2DAsync(dst, (size_t)dpitch, src, (size_t)spitch, (size_t)width, (size_t)height, k, (cudaStream_t)stream));
+    return ESP_OK;
+}

@@ -576,3 +576,62 @@ def test_graphed_decode_matches_kernel_by_kernel_decode_two_gpus(tmp_path):
             for a, b in zip(res["eager"]["logits"], res["graph"]["logits"]):
                 assert bool(torch.isfinite(b).all())
                 assert bool(((a - b).abs() <= 1e-3 + 1e-3 * a.abs()).all()), (a - b).abs().max()
+
+
+def _host_pipeline_worker(rank, world, port, out):
+    """Ring prefill from pinned host buffers, pipelined over chunks of heads, against the plain device-resident ring."""
+    dist, comm = _setup(rank, world, port)
+    from loongserve_b200 import context_attention as ca
+    from loongserve_b200 import ring
+    from loongserve_b200.host_pipeline import HostPrefillPipeline
+    dev = torch.device("cuda", rank)
+    g = torch.Generator().manual_seed(3)
+    lens = [1500, 130]
+    T, Hq, Hkv, D = sum(lens), 8, 4, 128
+    q = torch.randn(T, Hq, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+    local_len, first, stride = ring.shard_lengths(lens, world, True)
+    max_tok = max(sum(x) for x in local_len)
+    hq = O.shard_tokens(q, lens, world, True)[rank].contiguous().pin_memory()
+    hkv = torch.zeros(max_tok, 2 * Hkv, D, dtype=torch.bfloat16)
+    kr = O.shard_tokens(k, lens, world, True)[rank]; vr = O.shard_tokens(v, lens, world, True)[rank]
+    hkv[:kr.shape[0], :Hkv] = kr; hkv[:vr.shape[0], Hkv:] = vr
+    hkv = hkv.pin_memory()
+    ho = torch.zeros_like(hq).pin_memory()
+    metas = [ring.BlockMeta.from_lengths(local_len[r], first[r], dev) for r in range(world)]
+    pipe = HostPrefillPipeline(hq.shape[0], max_tok, Hq, Hkv, D, rank=rank, peers=list(range(world)), metas=metas, stride=stride,
+                               max_len_in_batch=max(local_len[rank]), comm=comm, head_chunks=2, device=dev)
+    pipe.run(hq, hkv, ho).synchronize()
+    ho.zero_()
+    pipe.run(hq, hkv, ho).synchronize()
+    dq, dkv = hq.to(dev), hkv.to(dev)
+    o = torch.empty_like(dq); m = torch.empty(dq.shape[0], Hq, device=dev); l = torch.empty(dq.shape[0], Hq, device=dev)
+    ring.ring_context_attention(dq, dkv, o, m, l, rank=rank, peers=list(range(world)), metas=metas, stride=stride,
+                                max_len_in_batch=max(local_len[rank]), num_kv_heads=Hkv, comm=comm,
+                                recv_buffers=[torch.empty_like(dkv), torch.empty_like(dkv)], attention_fn=ca.context_attention_fwd,
+                                init_fn=lambda o_, m_, l_: ca.init_attention_state(None, m_, l_))
+    torch.cuda.synchronize()
+    torch.save(dict(same=bool(torch.equal(ho.view(torch.int16), o.cpu().view(torch.int16))), o=ho.clone(), status=ca.device_status()),
+               os.path.join(out, f"hp{rank}.pt"))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+
+
+def test_host_pipeline_ring_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    mp.spawn(_host_pipeline_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    g = torch.Generator().manual_seed(3)
+    lens = [1500, 130]
+    T, Hq, Hkv, D = sum(lens), 8, 4, 128
+    q = torch.randn(T, Hq, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+    ro, _ = O.full_causal_attention(q, k, v, lens)
+    parts = [torch.load(os.path.join(str(tmp_path), f"hp{r}.pt")) for r in range(world)]
+    assert all(p["same"] and p["status"][0] == 0 for p in parts)
+    o = O.unshard_tokens([p["o"] for p in parts], lens, world, True)
+    assert bool(((o.float() - ro).abs() <= 2e-2 + 1e-2 * ro.abs()).all())
