@@ -306,37 +306,57 @@ class ESPAttentionRuntime:
                                      mp.global_mid_o, mp.global_mid_lse, mp.block_seq)
             return o
         qv = q.view(-1, self.tp_q_head_num_, self.head_dim_) if q is not None else None
-        grp = self._fused_group_for(st)
-        if grp is not None:
-            rtt = self.req_manager.req_to_token_indexs
-            if st.master_plan is not None:
-                mp = st.master_plan
-                n_other = len(mp.peers) - 1
-                res = grp.step(qv.contiguous(), pool_layer, rtt, self.tp_k_head_num_, mp.b_req_idx, mp.b_seq_len, mp.max_len_in_batch,
-                               mp.block_seq, mp.global_mid_o[n_other:], mp.global_mid_lse[n_other:], out=out, out_lse=mp.global_out_lse)
-                return res[0]
-            pp = st.peer_plan
-            grp.step(None, pool_layer, rtt, self.tp_k_head_num_, pp.peer_b_req_idx, pp.peer_b_seq_len, pp.peer_max_len_in_batch,
-                     pp.block_seq, pp.peer_mid_o, pp.peer_mid_lse)
-            return None
+        if self._fused_covers(st):
+            return self._token_attention_peer_memory(qv, st, pool_layer, out)
         return ringmod.multi_master_decode_attention(qv, pool_layer, self.req_manager.req_to_token_indexs, self.tp_k_head_num_,
                                                      self.sp_comm, self.total_rank_, st.master_plan, st.peer_plan,
                                                      fd.flash_decoding_stage1, fd.flash_decoding_stage2, out=out)
 
-    def _fused_group_for(self, st):
-        """The peer-memory group serving this batch, if one is enabled and the batch has exactly one master whose
-        peers are all instances (the group's layout assumes that)."""
+    def _fused_covers(self, st) -> bool:
+        """True when every master of this batch has a peer-memory group and the batch spans all instances
+        (the groups' layout assumes that)."""
         if not self._fused_groups:
-            return None
-        if st.master_plan is not None and st.peer_plan is None:
-            master = self.total_rank_
+            return False
+        masters = []
+        if st.master_plan is not None:
             if sorted(st.master_plan.peers) != list(range(self.sp_world_size)):
-                return None
-        elif st.peer_plan is not None and st.master_plan is None and len(st.peer_plan.masters) == 1:
-            master = st.peer_plan.masters[0]
-        else:
+                return False
+            masters.append(self.total_rank_)
+        if st.peer_plan is not None:
+            masters += list(st.peer_plan.masters)
+        return bool(masters) and all(m in self._fused_groups for m in masters)
+
+    def _token_attention_peer_memory(self, qv, st, pool_layer, out):
+        """The exchange of longserve_transformer_layer_infer.py:224-370 over peer memory: every master first pushes its
+        queries (so no instance waits for one that is itself waiting), then serves the other masters' mini-batches in the
+        order of ``peer_sp_master_rank_list``, then attends to its own tokens and merges."""
+        rtt, Hkv = self.req_manager.req_to_token_indexs, self.tp_k_head_num_
+        mp, pp = st.master_plan, st.peer_plan
+        groups = ([self._fused_groups[self.total_rank_]] if mp is not None else []) + \
+                 ([self._fused_groups[m] for m in pp.masters] if pp is not None else [])
+        for g in groups:
+            g.next_step()
+        if mp is not None:
+            own = self._fused_groups[self.total_rank_]
+            qv = qv.contiguous()
+            own.master_push(qv)
+        if pp is not None:
+            Hq, D = self.tp_q_head_num_, self.head_dim_
+            nblk = (pp.peer_max_len_in_batch + pp.block_seq - 1) // pp.block_seq
+            for m, (a, b) in zip(pp.masters, pp.ranges):
+                n = b - a
+                if n == 0:
+                    continue
+                mid_o = pp.peer_mid_o.view(-1)[:nblk * n * Hq * D].view(nblk, n, Hq, D)        # scratch reused master after master
+                mid_lse = pp.peer_mid_lse.view(-1)[:nblk * n * Hq].view(nblk, n, Hq)
+                self._fused_groups[m].peer_serve(pool_layer, rtt, Hkv, pp.peer_b_req_idx[a:b], pp.peer_b_seq_len[a:b],
+                                                 pp.peer_max_len_in_batch, pp.block_seq, mid_o, mid_lse)
+        if mp is None:
             return None
-        return self._fused_groups.get(master)
+        n_other = len(mp.peers) - 1
+        o, _ = own.master_finish(qv, pool_layer, rtt, Hkv, mp.b_req_idx, mp.b_seq_len, mp.max_len_in_batch, mp.block_seq,
+                                 mp.global_mid_o[n_other:], mp.global_mid_lse[n_other:], out=out, out_lse=mp.global_out_lse)
+        return o
 
     # ------------------------------------------------------------------------------------------ migration
     @torch.inference_mode()

@@ -291,7 +291,7 @@ def test_runtime_prefill_keep_decode_migrate_two_gpus(tmp_path):
     assert parts[0]["state_sum"] == sum(parts[0]["kept"]) + 150 and parts[1]["state_sum"] == sum(parts[1]["kept"]) - 150
 
 
-def _two_masters_worker(rank, world, port, out):
+def _two_masters_worker(rank, world, port, out, peer_memory=False):
     """Both instances are masters of their own mini-batch and peers for the other's
     (the multi-master case: pre_process.py:194-230, longserve_transformer_layer_infer.py:247-265)."""
     dist, comm = _setup(rank, world, port)
@@ -300,6 +300,13 @@ def _two_masters_worker(rank, world, port, out):
     Hq, Hkv, D = 8, 2, 128
     rt = ESPAttentionRuntime(layers_num=1, q_head_num=Hq, kv_head_num=Hkv, head_dim=D, max_total_token_num=8192, max_req_num=16,
                              max_seq_length=4096, sp_world_size=world, total_rank=rank, sp_comm=comm, dtype=torch.float16, device=dev)
+    if peer_memory:
+        def gather(b):
+            lst = [None] * world
+            dist.all_gather_object(lst, b)
+            return lst
+        for master in range(world):                 # one group per master, created in the same order everywhere
+            rt.enable_peer_memory_decode(master, gather, max_batch=4)
     g = torch.Generator().manual_seed(77)
     # requests 0..2 belong to master 0, requests 3..4 to master 1; lengths include the new token
     lens = [900, 33, 2000, 513, 1500]
@@ -329,18 +336,23 @@ def _two_masters_worker(rank, world, port, out):
     rt.decode_cache_kv(st, 0).copy_(new_rows)
     rt.post_decode_cache_kv(st, 0)
     o = rt.token_attention(q[my_reqs].to(dev), st, 0)
+    if peer_memory:
+        o = rt.token_attention(q[my_reqs].to(dev), st, 0)        # a second layer call: flags and slots are reused
     torch.cuda.synchronize()
-    torch.save(dict(o=o.cpu(), lse=st.global_out_logexpsum.cpu(), reqs=my_reqs), os.path.join(out, f"mm{rank}.pt"))
+    status = rt._fused_groups[rank].device_status() if peer_memory else (0, 0, 0, 0)
+    torch.save(dict(o=o.cpu(), lse=st.global_out_logexpsum.cpu(), reqs=my_reqs, status=status), os.path.join(out, f"mm{rank}.pt"))
     dist.barrier()
+    rt.close()
     comm.close()
     dist.destroy_process_group()
 
 
-def test_two_masters_two_gpus(tmp_path):
+@pytest.mark.parametrize("peer_memory", [False, True], ids=["nccl", "peer_memory"])
+def test_two_masters_two_gpus(tmp_path, peer_memory):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     world = 2
-    mp.spawn(_two_masters_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_two_masters_worker, args=(world, _free_port(), str(tmp_path), peer_memory), nprocs=world, join=True)
     g = torch.Generator().manual_seed(77)
     Hq, Hkv, D = 8, 2, 128
     lens = [900, 33, 2000, 513, 1500]
@@ -355,6 +367,7 @@ def test_two_masters_two_gpus(tmp_path):
     for r in range(world):
         p = torch.load(os.path.join(str(tmp_path), f"mm{r}.pt"))
         got, want = p["o"].float(), ro[p["reqs"]]
+        assert p["status"][0] == 0                                  # no flag wait ran out
         assert bool(((got - want).abs() <= 2e-2 + 1e-2 * want.abs()).all())
         assert torch.allclose(p["lse"], rl[p["reqs"]], atol=1e-3, rtol=1e-3)
 
