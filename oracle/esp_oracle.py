@@ -19,12 +19,18 @@ It restates, in plain fp32 torch/numpy on the CPU, the algorithms of the referen
   ``loongserve/common/basemodel/triton_kernel/copy_kv_index_to_req.py:8-18``,
   ``loongserve/common/infer_utils.py:1-13``,
   ``loongserve/models/llama/triton_kernel/decoding_stage_migration.py:6-69,98-158``;
-* the slot allocator order -- ``loongserve/common/longserve_mem_manager.py:32-89``.
+* the slot allocator order -- ``loongserve/common/longserve_mem_manager.py:32-89``;
+* the layer glue (RMSNorm, rotate-half RoPE, SiLU*mul, FFN block, one whole Llama layer) --
+  ``longserve_cuda_kernels/src/rms_norm.cu``, ``rotary_emb.cu``, ``silu_and_mul.cu``, ``entrypoints.cpp:89-101``,
+  ``loongserve/models/llama/layer_infer/longserve_transformer_layer_infer.py:70-96,372-456``;
+* the prefill scheduling search -- ``longserve_c_scheduler/src/main.cpp:34-86``.
 
 Parity status.  Pinned: the ring step, the full causal attention, every KV scatter / registration /
 migration function and the allocator are checked against golden vectors produced by running the
 reference's own code in this project's build container (``tests/golden/make_golden.py``: the Triton
-kernels under Triton's CPU interpreter, ``torch_att`` and the Python managers directly).
+kernels under Triton's CPU interpreter, ``torch_att`` and the Python managers directly); the scheduling
+search is checked, bit for bit, against tables from the reference's own C++ module compiled by
+``oracle/Makefile``.
 Flash-decoding stage 1/2 exist in the reference only as CUDA and have no reference test:
 their restatement is checked on a GPU against the reference kernels compiled by ``oracle/Makefile``;
 on the CPU their parity is unpinned and rests on the algebraic identity with full softmax attention.
