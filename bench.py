@@ -635,7 +635,7 @@ def main():
     ap.add_argument("--e2e-decode-steps", type=int, default=128)
     ap.add_argument("--e2e-layers", type=int, default=32)
     ap.add_argument("--e2e-head-chunks", type=int, default=0,
-                    help="head chunks of the pipelined host-buffer leg (default 8 on one GPU, 4 on two, else 2)")
+                    help="head chunks of the pipelined host-buffer leg (default 8 on one GPU, else 4)")
     ap.add_argument("--e2e-graph", action="store_true",
                     help="end-to-end run: replay the decode step as one CUDA graph per instance (implies --e2e-exchange peer_memory)")
     ap.add_argument("--e2e-exchange", default="nccl", choices=["nccl", "peer_memory"],
@@ -748,7 +748,7 @@ def main():
 
         # the public host-buffer call: chunks of heads pipelined over the copy engines and the ring
         from loongserve_b200.host_pipeline import HostPrefillPipeline
-        chunks = args.e2e_head_chunks or (8 if P == 1 else 4 if P == 2 else 2)
+        chunks = args.e2e_head_chunks or (8 if P == 1 else 4)
         o_sample = o[:512].clone()                   # rows of the device-resident run, to check the host-buffer result against
         del o, m, l
         recv.clear()
