@@ -80,3 +80,24 @@ def test_abi_version_matches_header_and_python_table(built):
 def test_build_entry_point_runs():
     import __graft_entry__ as g
     g.build()
+
+
+def test_headers_compile_as_plain_c_and_link(tmp_path, built):
+    """The boundary is a C ABI: both headers must be usable from a C99 translation unit, and a C program linked against
+    the library must resolve and call a symbol (no device work: the version query)."""
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("gcc not available")
+    src = tmp_path / "abi.c"
+    src.write_text('#include "esp_attention.h"\n#include "esp_rnccl.h"\n'
+                   'int main(void) { return esp_abi_version() == ESP_ABI_VERSION ? 0 : 1; }\n')
+    exe = tmp_path / "abi"
+    libdir = os.path.dirname(built.ATTN_LIB)
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                    "-L", libdir, "-l:libesp_attention.so", f"-Wl,-rpath,{libdir}"], check=True)
+    env = dict(os.environ)
+    import torch
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    env["LD_LIBRARY_PATH"] = os.pathsep.join([torch_lib, "/usr/local/cuda/lib64", env.get("LD_LIBRARY_PATH", "")])
+    assert subprocess.run([str(exe)], env=env).returncode == 0
