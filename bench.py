@@ -392,7 +392,7 @@ def e2e_llama(args):
     rt = ESPAttentionRuntime(layers_num=cfg.num_layers, q_head_num=cfg.num_q_heads, kv_head_num=cfg.num_kv_heads,
                              head_dim=cfg.head_dim, max_total_token_num=max_tok + steps + 64, max_req_num=4,
                              max_seq_length=max_tok + steps + 64, sp_world_size=P, total_rank=rank, sp_comm=comm,
-                             dtype=torch.bfloat16, device=dev, decode_block_seq=1024, host_side_allocator=bool(args.e2e_graph))
+                             dtype=torch.bfloat16, device=dev, decode_block_seq=1024)
     stack = LlamaESPStack(cfg, LlamaWeights(cfg, torch.bfloat16, dev, seed=0), rt)
     if args.e2e_exchange == "peer_memory" and world > 1:
         def gather(b):

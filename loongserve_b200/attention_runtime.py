@@ -19,7 +19,7 @@ from . import context_attention as ca
 from . import flash_decoding as fd
 from . import kv_ops
 from . import ring as ringmod
-from .mem_manager import LongServeMemoryManager, LongServeReqManager, SyncFreeMemoryManager
+from .mem_manager import LongServeMemoryManager, LongServeReqManager
 
 
 def next_power_of_2(n: int) -> int:
@@ -38,8 +38,7 @@ class ESPAttentionRuntime:
 
     def __init__(self, *, layers_num: int, q_head_num: int, kv_head_num: int, head_dim: int, max_total_token_num: int,
                  max_req_num: int, max_seq_length: int, sp_world_size: int = 1, total_rank: int = 0, sp_comm=None,
-                 dtype=torch.bfloat16, device="cuda", decode_block_seq: Optional[int] = None,
-                 host_side_allocator: bool = False):
+                 dtype=torch.bfloat16, device="cuda", decode_block_seq: Optional[int] = None):
         self.layers_num = layers_num
         self.tp_q_head_num_ = q_head_num
         self.tp_k_head_num_ = kv_head_num
@@ -52,10 +51,8 @@ class ESPAttentionRuntime:
         self.device = torch.device(device)
         self.decode_block_seq = decode_block_seq
         # longserve_model.py:120-133: sp_world_size spare rows are appended to the pool and never handed out
-        # host_side_allocator: same slot order, decisions taken on the host without device round trips
-        mm_cls = SyncFreeMemoryManager if host_side_allocator else LongServeMemoryManager
-        self.mem_manager = mm_cls(max_total_token_num, dtype, kv_head_num, head_dim, layers_num,
-                                  num_idle_slots=sp_world_size, device=device)
+        self.mem_manager = LongServeMemoryManager(max_total_token_num, dtype, kv_head_num, head_dim, layers_num,
+                                                  num_idle_slots=sp_world_size, device=device)
         self.req_manager = LongServeReqManager(max_req_num, max_seq_length, self.mem_manager)
         self._fused_groups = {}
 
@@ -381,15 +378,11 @@ class ESPAttentionRuntime:
                                                           max_migration_len)
             self.sp_comm.wait_for_default_stream()
             self.sp_comm.nccl_send(buf, peer_sp_rank)
-            if isinstance(self.mem_manager, SyncFreeMemoryManager):
-                # the kernel zeroed the device reference counts; tell the host allocator which slots those were
-                # (a device->host read, acceptable here: migration is not on the per-step path)
-                rt_, ids = self.req_manager.req_to_token_indexs, []
-                for b in range(b_req_idx.shape[0]):
-                    n, L = int(b_migration_len[b]), int(b_seq_len[b])
-                    if n:
-                        ids.append(rt_[int(b_req_idx[b]), L - n:L])
-                self.mem_manager._host.decrease_refs(torch.cat(ids).long())
-                self.mem_manager.can_use_mem_size = self.mem_manager._host.can_use
-            else:
-                self.mem_manager.can_use_mem_size += total
+            # the kernel zeroed the device reference counts; tell the host allocator which slots those were
+            # (a device->host read, acceptable here: migration is not on the per-step path)
+            rt_, ids = self.req_manager.req_to_token_indexs, []
+            lens_h, mig_h, req_h = b_seq_len.tolist(), b_migration_len.tolist(), b_req_idx.tolist()
+            for rid, n, L in zip(req_h, mig_h, lens_h):
+                if n:
+                    ids.append(rt_[rid, L - n:L])
+            self.mem_manager.release_on_host(torch.cat(ids))

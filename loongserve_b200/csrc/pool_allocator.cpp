@@ -90,9 +90,10 @@ extern "C" int esp_pool_alloc_contiguous(esp_pool* p, int64_t n, int64_t* start)
 
 extern "C" int esp_pool_add_refs(esp_pool* p, const int64_t* ids, int64_t n) {
     if (!p || n < 0 || (n > 0 && !ids)) return ESP_ERR_BAD_ARG;
+    for (int64_t i = 0; i < n; ++i)
+        if (ids[i] < 0 || ids[i] >= p->size) return ESP_ERR_BAD_ARG;      // checked before anything changes
     for (int64_t i = 0; i < n; ++i) {
         const int64_t s = ids[i];
-        if (s < 0 || s >= p->size) return ESP_ERR_BAD_ARG;
         if (p->refs[s]++ == 0) { clr_free(p, s); --p->free_count; }
     }
     return ESP_OK;
@@ -100,9 +101,20 @@ extern "C" int esp_pool_add_refs(esp_pool* p, const int64_t* ids, int64_t n) {
 
 extern "C" int esp_pool_decrease_refs(esp_pool* p, const int64_t* ids, int64_t n) {
     if (!p || n < 0 || (n > 0 && !ids)) return ESP_ERR_BAD_ARG;
+    // nothing is changed unless the whole request is valid; a slot may appear several times in `ids`
     for (int64_t i = 0; i < n; ++i) {
         const int64_t s = ids[i];
-        if (s < 0 || s >= p->size) return ESP_ERR_BAD_ARG;
+        if (s < 0 || s >= p->size || p->refs[s] <= 0) return ESP_ERR_BAD_ARG;
+    }
+    for (int64_t i = 0; i < n; ++i) {
+        const int64_t s = ids[i];
+        if (p->refs[s] <= 0) {        // released more often in this call than it was held: undo and refuse
+            for (int64_t k = 0; k < i; ++k) {
+                const int64_t u = ids[k];
+                if (p->refs[u]++ == 0) { clr_free(p, u); --p->free_count; }
+            }
+            return ESP_ERR_BAD_ARG;
+        }
         if (--p->refs[s] == 0) {
             set_free(p, s);
             ++p->free_count;

@@ -445,8 +445,7 @@ def _forward_kwargs_worker(rank, world, port, out):
     dev = torch.device("cuda", rank)
     cfg = LlamaConfig(num_layers=2, hidden=512, num_q_heads=4, num_kv_heads=4, head_dim=128, ffn=1024, vocab=1000)
     rt = ESPAttentionRuntime(layers_num=2, q_head_num=4, kv_head_num=4, head_dim=128, max_total_token_num=2048, max_req_num=8,
-                             max_seq_length=2048, sp_world_size=world, total_rank=rank, sp_comm=comm, dtype=torch.bfloat16, device=dev,
-                             host_side_allocator=True)
+                             max_seq_length=2048, sp_world_size=world, total_rank=rank, sp_comm=comm, dtype=torch.bfloat16, device=dev)
     stack = LlamaESPStack(cfg, LlamaWeights(cfg, torch.bfloat16, dev, seed=3), rt)
     g = torch.Generator().manual_seed(9)
     full = [301, 64, 130]
@@ -535,7 +534,7 @@ def _graphed_decode_worker(rank, world, port, out):
     for mode in ("eager", "graph"):
         rt = ESPAttentionRuntime(layers_num=cfg.num_layers, q_head_num=4, kv_head_num=2, head_dim=128, max_total_token_num=2048,
                                  max_req_num=8, max_seq_length=2048, sp_world_size=world, total_rank=rank, sp_comm=comm,
-                                 dtype=torch.bfloat16, device=dev, decode_block_seq=256, host_side_allocator=True)
+                                 dtype=torch.bfloat16, device=dev, decode_block_seq=256)
         rt.enable_peer_memory_decode(0, gather, max_batch=B)
         stack = LlamaESPStack(cfg, weights, rt)
         st = rt.prepare_prefill(B, sum(b_len), max_tok, max(b_len), i32([0, 1]), i32([0, b_len[0]]), i32(b_len), i32([rank] * B),

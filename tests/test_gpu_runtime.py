@@ -15,13 +15,12 @@ def _check(o, ro):
     assert bool(((o - ro).abs() <= 2e-2 + 1e-2 * ro.abs()).all()), (o - ro).abs().max()
 
 
-@pytest.mark.parametrize("host_alloc", [False, True])
 @pytest.mark.parametrize("fragment_pool", [False, True])
-def test_prefill_then_decode_single_instance(fragment_pool, host_alloc):
+def test_prefill_then_decode_single_instance(fragment_pool):
     from loongserve_b200.attention_runtime import ESPAttentionRuntime
     L, Hq, Hkv, D = 2, 8, 2, 128
     rt = ESPAttentionRuntime(layers_num=L, q_head_num=Hq, kv_head_num=Hkv, head_dim=D, max_total_token_num=2048,
-                             max_req_num=8, max_seq_length=512, dtype=torch.bfloat16, host_side_allocator=host_alloc)
+                             max_req_num=8, max_seq_length=512, dtype=torch.bfloat16)
     if fragment_pool:
         # leave no contiguous run long enough: occupy every 64th slot
         hold = rt.mem_manager.alloc(2048)

@@ -187,9 +187,9 @@ def test_multi_master_decode_world2_gloo(tmp_path):
 def test_host_side_allocator_matches_reference_trace_and_oracle(golden_dir):
     """The native host allocator reproduces the reference-generated golden trace and, over a random sequence of
     operations, the oracle's restatement of the reference allocator, slot for slot."""
-    from loongserve_b200.mem_manager import HostSlotAllocator, SyncFreeMemoryManager
+    from loongserve_b200.mem_manager import HostSlotAllocator, LongServeMemoryManager
     g = np.load(os.path.join(golden_dir, "mem_manager.npz"))
-    mm = SyncFreeMemoryManager(64, torch.float16, 2, 8, 1, device="cpu")
+    mm = LongServeMemoryManager(64, torch.float16, 2, 8, 1, device="cpu")
     a = mm.alloc(5)
     assert np.array_equal(a.numpy(), g["t0_alloc5"]) and mm.can_use_mem_size == int(g["t0_free"])
     b = mm.alloc_contiguous(7)
@@ -207,7 +207,7 @@ def test_host_side_allocator_matches_reference_trace_and_oracle(golden_dir):
     assert mm.alloc_contiguous(60) is None
     with pytest.raises(RuntimeError, match="not enough KV cache"):
         mm.alloc(10_000)
-    assert np.array_equal(mm._host.state().numpy(), mm.mem_state.numpy())
+    assert np.array_equal(mm._slots.state().numpy(), mm.mem_state.numpy())
     # randomised comparison with the oracle
     rng = np.random.default_rng(0)
     size = 700
@@ -236,6 +236,34 @@ def test_host_side_allocator_matches_reference_trace_and_oracle(golden_dir):
         if step % 50 == 0:
             assert np.array_equal(host.state().numpy(), ora.mem_state)
     assert np.array_equal(host.state().numpy(), ora.mem_state)
+
+
+def test_pool_manager_duplicates_resize_and_over_release():
+    """Ids listed twice count once (an index update on the device applies once per distinct slot); resize_mem starts a
+    fresh pool of the new size on the host and on the device alike; releasing a slot that holds no reference is an
+    error and changes nothing."""
+    from loongserve_b200.mem_manager import LongServeMemoryManager, LongServeReqManager
+    mm = LongServeMemoryManager(32, torch.float16, 1, 8, 1, device="cpu")
+    a = mm.alloc(4)
+    mm.add_refs(torch.tensor([1, 1, 2]))
+    assert mm.mem_state[:4].tolist() == [1, 2, 2, 1] and np.array_equal(mm._slots.state().numpy(), mm.mem_state.numpy())
+    mm.free(torch.tensor([1, 1, 2], dtype=torch.int32))
+    assert mm.mem_state[:4].tolist() == [1, 1, 1, 1] and mm.can_use_mem_size == 28
+    with pytest.raises(RuntimeError):
+        mm._slots.decrease_refs(torch.tensor([0, 9]))          # slot 9 holds nothing
+    assert mm.can_use_mem_size == 28 and mm._slots.state()[0] == 1
+    mm.resize_mem(48)
+    assert mm.can_use_mem_size == 48 and mm.mem_state.shape[0] == 48 and mm.kv_buffer.shape[1] == 48
+    assert mm.alloc(40).tolist() == list(range(40)) and mm.alloc_contiguous(8)[1:] == (40, 48)
+    rm = LongServeReqManager(4, 16, mm)
+    r = rm.alloc(3)
+    assert r.tolist() == [0, 1, 2] and rm.can_use_req_size == 1 and rm.alloc(2) is None
+    rm.free_req(1)
+    rm.free(torch.tensor([0]), None)
+    assert rm.can_use_req_size == 3 and rm.req_state.tolist() == [False, False, True, False]
+    assert rm.alloc(2).tolist() == [0, 1]
+    rm.free_all()
+    assert rm.can_use_req_size == 4 and not rm.req_state.any()
 
 
 def test_migration_chunker_order_and_bookkeeping():
