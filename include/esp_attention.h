@@ -25,6 +25,7 @@ extern "C" {
 #define ESP_ERR_UNSUPPORTED (-5)    /* valid request the library has no kernel for */
 #define ESP_ERR_NCCL (-6)           /* an NCCL call failed */
 #define ESP_ERR_TOO_LARGE (-7)      /* size beyond a fixed capacity stated by the entry point */
+#define ESP_ERR_BAD_SLOT (-8)       /* a kernel met a slot id outside the pool and skipped that row (device status words) */
 
 #define ESP_DTYPE_F16 0
 #define ESP_DTYPE_BF16 1
@@ -33,8 +34,9 @@ extern "C" {
 const char* esp_strerror(int code);
 /* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
 const char* esp_last_cuda_error(void);
-/* ABI version of this header (bumped on incompatible change).  Version 2: the peer-memory entry points take `value_base`. */
-#define ESP_ABI_VERSION 2
+/* ABI version of this header (bumped on incompatible change).  Version 2: the peer-memory entry points take `value_base`.
+ * Version 3: the kernels that dereference slot ids take the pool's row count; the self-test kernels left the library. */
+#define ESP_ABI_VERSION 3
 int esp_abi_version(void);
 
 /* ------------------------------------------------------------------------------------------------
@@ -82,6 +84,11 @@ int esp_prefill_lse(const float* m, const float* l, float* lse, int64_t n, void*
  * Synchronises the device.  `clear` != 0 resets it. */
 int esp_device_status(int32_t out[4], int32_t clear);
 
+/* Limit, in SM cycles, of every bounded in-kernel wait of this library on the CURRENT device (the mbarrier waits of the
+ * prefill kernel, the flag waits of the gated decode kernels and of esp_flag_wait).  Default 2e9 (about a second).
+ * The reference has no counterpart: its kernels never wait on one another, and its NCCL calls wait without a limit. */
+int esp_set_wait_limit_cycles(int64_t cycles);
+
 /* ------------------------------------------------------------------------------------------------
  * Distributed flash-decoding.
  * esp_decode_stage1 replaces longserve_cuda_kernels.flash_decoding_stage1
@@ -92,6 +99,9 @@ int esp_device_status(int32_t out[4], int32_t clear);
  * Block j of request b covers tokens [j*seq_block_size, min((j+1)*seq_block_size, len_b)); blocks
  * past the length are not written.  Unlike the reference seq_block_size may be any positive value
  * (the reference caps it at 256); head_dim must be 128.
+ * pool_rows: number of slot rows k and v have.  A slot id outside [0, pool_rows) -- the table's 2147483647 filler
+ * included -- is not dereferenced: the token is left out, and esp_decode_device_status reports ESP_ERR_BAD_SLOT with
+ * the id.  pool_rows <= 0 switches the check off (the reference has none: longserve_req_manager.py:19 is the filler).
  */
 int esp_decode_stage1(float* mid_o, float* mid_lse, const void* q, const void* k, const void* v,
                       int64_t k_stride_t, int64_t k_stride_h, int64_t v_stride_t, int64_t v_stride_h,
@@ -99,7 +109,7 @@ int esp_decode_stage1(float* mid_o, float* mid_lse, const void* q, const void* k
                       const int32_t* b_req_idx, const int32_t* b_seqlen, int32_t batch,
                       int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
                       int32_t max_len_in_batch, int32_t seq_block_size, int32_t dtype, float sm_scale,
-                      void* stream);
+                      int64_t pool_rows, void* stream);
 
 /* esp_decode_merge replaces longserve_cuda_kernels.flash_decoding_stage2
  *   (entrypoints.cpp:166-221, flash_decoding_stage2.cu:15-150): lse-merge of
@@ -118,7 +128,8 @@ int esp_decode_merge(void* o, float* out_lse, const int32_t* b_seqlen, const flo
  * capacity the call returns ESP_ERR_TOO_LARGE and launches nothing.  The call itself performs no
  * cudaMalloc / cudaFree.  Its first call on a device looks up the array's device address (once per
  * device, with that device current): make that first call before any stream capture.  Every call on a
- * device shares the array, so calls that overlap on the GPU race; calls on one stream are safe.
+ * device shares the array, so calls that overlap on the GPU race; calls on one stream are safe.  The array used is the
+ * one of the device that is CURRENT when the call is made, so `stream` must belong to the current device.
  * Arguments as esp_decode_stage1 / esp_decode_merge; o_dtype F16/BF16/F32. */
 int esp_decode_attention_noalloc(void* o, float* out_lse, const void* q, const void* k, const void* v,
                                  int64_t k_stride_t, int64_t k_stride_h, int64_t v_stride_t,
@@ -126,7 +137,7 @@ int esp_decode_attention_noalloc(void* o, float* out_lse, const void* q, const v
                                  int64_t req_to_tokens_stride, const int32_t* b_req_idx,
                                  const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
                                  int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
-                                 int32_t dtype, int32_t o_dtype, float sm_scale, void* stream);
+                                 int32_t dtype, int32_t o_dtype, float sm_scale, int64_t pool_rows, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Distributed decode over peer memory (NVLink loads/stores instead of NCCL messages).  The reference moves the
@@ -155,8 +166,21 @@ int esp_peer_buffer_destroy(void* dev_ptr);
  * pointers, host arrays of device pointers), then store flag_value (+ *value_base) to each peer's flag with release semantics. */
 int esp_peer_push(const void* src, void* const* peer_dst, int32_t* const* peer_flags, int32_t n_peers,
                   int64_t bytes, int32_t flag_value, const int32_t* value_base, void* stream);
-/* Publish everything this stream has written so far to the owner of remote_flag: *remote_flag = value (+ *value_base). */
+/* Publish everything this stream has written so far to the owner of remote_flag: *remote_flag = value (+ *value_base).
+ * Nothing is published while the device's status word holds a timed-out wait: the kernels behind that wait returned
+ * without writing their results, so the other side times out as well instead of consuming them. */
 int esp_peer_signal(int32_t* remote_flag, int32_t value, const int32_t* value_base, void* stream);
+/* A one-thread kernel that waits until *flag >= value (+ *value_base); work queued behind it on `stream` starts only
+ * then.  The wait is bounded: it gives up after `patience` (1..1000) times the device's wait limit
+ * (esp_set_wait_limit_cycles), and esp_decode_device_status then reports ESP_ERR_DEVICE_TIMEOUT with `wait_id` (>= 16,
+ * the caller's label for this wait) and the awaited value.  Used by the copy-engine ring exchange; the reference's
+ * ring waits inside ncclRecv, without a limit (longserve_transformer_layer_infer.py:162-178). */
+int esp_flag_wait(const int32_t* flag, int32_t value, const int32_t* value_base, int32_t wait_id, int32_t patience,
+                  void* stream);
+/* cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault) on `stream`: a copy-engine transfer; dst or src may be a peer's
+ * buffer mapped with esp_peer_buffer_open.  The reference moves KV blocks with ncclSend/ncclRecv
+ * (rnccl/src/main.cpp:200-232), which copy with SM kernels. */
+int esp_memcpy_async(void* dst, const void* src, int64_t bytes, void* stream);
 
 /* esp_decode_stage1 whose blocks first wait until *wait_flag >= wait_value + *value_base (q then lives in a buffer the
  * master pushed into) and read q past the L1 cache. */
@@ -166,7 +190,7 @@ int esp_decode_stage1_gated(float* mid_o, float* mid_lse, const void* q, const v
                             int64_t req_to_tokens_stride, const int32_t* b_req_idx,
                             const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
                             int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
-                            int32_t seq_block_size, int32_t dtype, float sm_scale,
+                            int32_t seq_block_size, int32_t dtype, float sm_scale, int64_t pool_rows,
                             const int32_t* wait_flag, int32_t wait_value, const int32_t* value_base, void* stream);
 /* esp_decode_merge whose blocks first wait until wait_flags[i] >= wait_value + *value_base for all i < n_wait. */
 int esp_decode_merge_gated(void* o, float* out_lse, const int32_t* b_seqlen, const float* mid_o,
@@ -174,20 +198,30 @@ int esp_decode_merge_gated(void* o, float* out_lse, const int32_t* b_seqlen, con
                            int32_t num_blocks, int32_t block_seq, int32_t o_dtype,
                            const int32_t* wait_flags, int32_t n_wait, int32_t wait_value, const int32_t* value_base,
                            void* stream);
-/* Status of the bounded flag waits on the current device, like esp_device_status. */
+/* Status of the decode kernels and flag waits on the current device, like esp_device_status: out[0] = 0,
+ * ESP_ERR_DEVICE_TIMEOUT (out[2] = which wait: 1 stage-1 gate, 2 merge gate, >= 16 esp_flag_wait ids; out[3] = awaited
+ * value) or ESP_ERR_BAD_SLOT (out[3] = the slot id stage 1 refused).  After a timeout every later gated kernel on the
+ * device returns at once until the status is cleared. */
 int esp_decode_device_status(int32_t out[4], int32_t clear);
 
 /* ------------------------------------------------------------------------------------------------
  * Token-indexed KV pool: scatter, registration, migration (all bit-exact copies / integer work).
  * Rows are [heads2, D] with D contiguous; `row_stride` = token stride, `head_stride` = head stride.
  * `elem_bytes` is 2 for fp16/bf16.  Index arrays may be int32 or int64 (`idx64` != 0).
+ * `pool_rows` is the number of slot rows of the pool tensor a kernel indexes with slot ids: an id outside
+ * [0, pool_rows) is never dereferenced, its row is skipped and esp_kv_device_status reports it
+ * (pool_rows <= 0 switches the check off; the reference has no such check).
  */
+
+/* out[0] = 0 or ESP_ERR_BAD_SLOT, out[1] = kernel (1 scatter, 2 scatter+register, 3 migration gather, 4 migration
+ * scatter), out[2] = position of the id in its index array, out[3] = the id.  Synchronises the device. */
+int esp_kv_device_status(int32_t out[4], int32_t clear);
 
 /* out[dest[i]] = src[i], i < n.  Replaces destindex_copy_kv
  *   (loongserve/common/basemodel/triton_kernel/destindex_copy_kv.py:32-51). */
 int esp_kv_scatter(const void* src, int64_t src_row_stride, int64_t src_head_stride, void* out,
                    int64_t out_row_stride, int64_t out_head_stride, const void* dest, int32_t idx64,
-                   int64_t n, int32_t heads2, int32_t head_dim, int32_t elem_bytes, void* stream);
+                   int64_t n, int32_t heads2, int32_t head_dim, int32_t elem_bytes, int64_t pool_rows, void* stream);
 
 /* Keep-range of a passing striped block: begin = ceil((cache_begin - kv_first)/P), end likewise,
  * new_len = end - begin.  Replaces pre_copy_and_register_kv
@@ -209,7 +243,7 @@ int esp_kv_scatter_register(int32_t batch, const int32_t* new_len, const int32_t
                             int64_t req_to_token_stride, const int32_t* b_req_idx,
                             int64_t num_used_mem_index, int32_t max_len_in_batch,
                             int32_t should_register, int32_t heads2, int32_t head_dim,
-                            int32_t elem_bytes, void* stream);
+                            int32_t elem_bytes, int64_t pool_rows, void* stream);
 
 /* req_to_token[b_req_idx[i], b_seq_len[i]-1] = memindex[i].  Replaces copy_kv_index_to_req
  *   (loongserve/common/basemodel/triton_kernel/copy_kv_index_to_req.py:22-38). */
@@ -236,7 +270,7 @@ int esp_mig_gather(void* send_buf, int64_t total_tokens, const int32_t* req_to_t
                    const int32_t* num_tokens, const int64_t* num_tokens_cumsum,
                    const int32_t* b_seq_len, int32_t batch, int32_t max_num_tokens,
                    int32_t num_layers, int32_t heads2, int32_t head_dim, int32_t elem_bytes,
-                   void* stream);
+                   int64_t pool_rows, void* stream);
 
 /* Receiver side: scatter recv_buf into slots alloc_mem[cumsum_prev[b] + i] (all layers) and append
  * the slot ids at req_to_token[request_ids[b], b_seq_len[b] + i].  Replaces
@@ -247,7 +281,7 @@ int esp_mig_scatter(const void* recv_buf, int64_t total_tokens, int32_t* req_to_
                     const int32_t* request_ids, const int32_t* num_tokens,
                     const int64_t* num_tokens_cumsum, const int32_t* b_seq_len, int32_t batch,
                     int32_t max_num_tokens, int32_t num_layers, int32_t heads2, int32_t head_dim,
-                    int32_t elem_bytes, void* stream);
+                    int32_t elem_bytes, int64_t pool_rows, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Host-side slot allocator with the allocation order of LongServeMemoryManager
@@ -324,22 +358,6 @@ int esp_rotary_emb(void* x, const void* cosv, const void* sinv, int64_t x_stride
  * longserve_cuda_kernels.silu_and_mul_inplace (entrypoints.cpp:40-51, silu_and_mul.cu:17-45). */
 int esp_silu_and_mul_inplace(void* io, int64_t tokens, int32_t ffn_inter_dim, int32_t dtype,
                              void* stream);
-
-/* ------------------------------------------------------------------------------------------------
- * Building-block self check (used by the test-suite): D[128,128] fp32 = A[128,128] * B^T through one
- * tcgen05.mma chain, in the three operand forms the prefill kernel uses.
- * mode 0: A and B K-major in shared memory (the Q*K^T form);
- * mode 1: A K-major, B MN-major in shared memory (B given as [K=128, N=128] row-major, the P*V form);
- * mode 2: A converted to 16-bit and staged in tensor memory, B MN-major (the P*V form actually used).
- * a, b are device [128,128] of `dtype` row-major; d device fp32 [128,128]. */
-int esp_selftest_umma(const void* a, const void* b, float* d, int32_t mode, int32_t dtype,
-                      void* stream);
-
-/* Self check of the bounded-wait pattern every in-kernel wait of this library follows: a one-block kernel
- * waits on an mbarrier that nothing ever completes, for at most `limit_cycles` SM cycles (<= 4e9), then
- * writes 1 to *result_dev (device int) and returns normally; the context stays usable.  (2 would mean the
- * barrier completed, which cannot happen.) */
-int esp_selftest_bounded_wait(int64_t limit_cycles, int32_t* result_dev, void* stream);
 
 #ifdef __cplusplus
 }

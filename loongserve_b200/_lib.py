@@ -18,7 +18,7 @@ ESP_DTYPE_F16, ESP_DTYPE_BF16, ESP_DTYPE_F32 = 0, 1, 2
 _i32, _i64, _f32, _vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
 
 # name -> argtypes, exactly as declared in include/esp_attention.h
-ESP_ABI_VERSION = 2      # what esp_abi_version() of a matching library returns (see include/esp_attention.h)
+ESP_ABI_VERSION = 3      # what esp_abi_version() of a matching library returns (see include/esp_attention.h)
 
 ATTN_SIGNATURES = {
     "esp_abi_version": [],
@@ -27,31 +27,35 @@ ATTN_SIGNATURES = {
     "esp_prefill_state_init": [_vp, _i64, _vp, _vp, _i64, _vp],
     "esp_prefill_lse": [_vp, _vp, _vp, _i64, _vp],
     "esp_device_status": [C.POINTER(_i32), _i32],
+    "esp_set_wait_limit_cycles": [_i64],
     "esp_decode_stage1": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _vp,
-                          _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
+                          _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _i64, _vp],
     "esp_decode_merge": [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp],
     "esp_decode_attention_noalloc": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _vp,
-                                     _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
+                                     _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _i64, _vp],
     "esp_peer_buffer_create": [_i64, C.POINTER(_vp), C.POINTER(C.c_uint8)],
     "esp_peer_buffer_open": [C.POINTER(C.c_uint8), C.POINTER(_vp)],
     "esp_peer_buffer_close": [_vp],
     "esp_peer_buffer_destroy": [_vp],
     "esp_peer_push": [_vp, C.POINTER(_vp), C.POINTER(_vp), _i32, _i64, _i32, _vp, _vp],
     "esp_peer_signal": [_vp, _i32, _vp, _vp],
+    "esp_flag_wait": [_vp, _i32, _vp, _i32, _i32, _vp],
+    "esp_memcpy_async": [_vp, _vp, _i64, _vp],
+    "esp_kv_device_status": [C.POINTER(_i32), _i32],
     "esp_decode_stage1_gated": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _vp,
-                                _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _i32, _vp, _vp],
+                                _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _i64, _vp, _i32, _vp, _vp],
     "esp_decode_merge_gated": [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _vp, _vp],
     "esp_decode_device_status": [C.POINTER(_i32), _i32],
-    "esp_kv_scatter": [_vp, _i64, _i64, _vp, _i64, _i64, _vp, _i32, _i64, _i32, _i32, _i32, _vp],
+    "esp_kv_scatter": [_vp, _i64, _i64, _vp, _i64, _i64, _vp, _i32, _i64, _i32, _i32, _i32, _i64, _vp],
     "esp_kv_keep_range": [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp],
     "esp_kv_scatter_register": [_i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i32, _vp, _i64,
-                                _i64, _vp, _i64, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp],
+                                _i64, _vp, _i64, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i64, _vp],
     "esp_kv_index_register": [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _vp],
     "esp_kv_index_init": [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _vp],
     "esp_mig_gather": [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
-                       _i32, _i32, _i32, _vp],
+                       _i32, _i32, _i32, _i64, _vp],
     "esp_mig_scatter": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32,
-                        _i32, _i32, _i32, _i32, _vp],
+                        _i32, _i32, _i32, _i32, _i64, _vp],
     "esp_pool_create": [_i64, C.POINTER(_vp)],
     "esp_pool_destroy": [_vp],
     "esp_pool_alloc": [_vp, _i64, _vp],
@@ -66,8 +70,6 @@ ATTN_SIGNATURES = {
     "esp_rms_norm": [_vp, _vp, _vp, _i64, _i32, _f32, _i32, _vp],
     "esp_rotary_emb": [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _vp],
     "esp_silu_and_mul_inplace": [_vp, _i64, _i32, _i32, _vp],
-    "esp_selftest_umma": [_vp, _vp, _vp, _i32, _i32, _vp],
-    "esp_selftest_bounded_wait": [_i64, _vp, _vp],
 }
 ATTN_STRING_FUNCS = {"esp_strerror": [_i32], "esp_last_cuda_error": []}
 

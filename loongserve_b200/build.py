@@ -6,6 +6,8 @@ Produces, next to this file:
   libesp_attention.so  -- kernels + C ABI declared in include/esp_attention.h
   libesp_rnccl.so      -- raw NCCL point-to-point layer declared in include/esp_rnccl.h
 Both link the shared CUDA runtime, so they use the same runtime instance as PyTorch in one process.
+`build_selftest()` builds the test-suite's own kernels (tests/csrc/selftest_kernels.cu) into tests/libesp_selftest.so;
+they are not part of the product library.
 """
 from __future__ import annotations
 
@@ -18,7 +20,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 ROOT = os.path.dirname(HERE)
 
-ATTN_SOURCES = ["kv_scatter.cu", "decode_attention.cu", "prefill_attention.cu", "selftest_umma.cu", "layer_ops.cu",
+ATTN_SOURCES = ["kv_scatter.cu", "decode_attention.cu", "prefill_attention.cu", "layer_ops.cu",
                 "pool_allocator.cpp", "prefill_scheduler.cpp"]
 ATTN_LIB = os.path.join(HERE, "libesp_attention.so")
 RNCCL_LIB = os.path.join(HERE, "libesp_rnccl.so")
@@ -64,6 +66,17 @@ def build_attention(force: bool = False, verbose_ptxas: bool = False) -> str:
     return ATTN_LIB
 
 
+SELFTEST_SRC = os.path.join(ROOT, "tests", "csrc", "selftest_kernels.cu")
+SELFTEST_LIB = os.path.join(ROOT, "tests", "libesp_selftest.so")
+
+
+def build_selftest(force: bool = False) -> str:
+    deps = [SELFTEST_SRC] + [os.path.join(CSRC, h) for h in ("esp_common.cuh", "sm100_ptx.cuh")]
+    if force or _newer(SELFTEST_LIB, deps):
+        _run([_nvcc()] + NVCC_FLAGS + ["-shared", SELFTEST_SRC, "-o", SELFTEST_LIB])
+    return SELFTEST_LIB
+
+
 def build_rnccl(force: bool = False) -> str:
     src = os.path.join(CSRC, "rnccl.cpp")
     deps = [src, os.path.join(ROOT, "include", "esp_rnccl.h")]
@@ -77,6 +90,8 @@ def build_rnccl(force: bool = False) -> str:
 def build_all(force: bool = False) -> None:
     build_attention(force)
     build_rnccl(force)
+    if os.path.exists(SELFTEST_SRC):
+        build_selftest(force)
 
 
 if __name__ == "__main__":

@@ -18,9 +18,12 @@ constexpr int kDecUnroll = 4;             // tokens per half-warp per step
 constexpr int kDecChunk = 1024;           // slot ids staged in shared memory per chunk
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr long long kGateLimitCycles = 2000000000LL;   // about a second: bound of every cross-GPU flag wait
+// Bound of every cross-GPU flag wait in SM cycles (about a second by default); esp_set_wait_limit_cycles changes it.
+__device__ long long g_gate_limit_cycles = 2000000000LL;
 
-// Status of the bounded flag waits of the gated (peer-memory) decode kernels: {code, block, which, value}.
+// Status of this file's kernels: {code, block, which, value}.  code ESP_ERR_DEVICE_TIMEOUT: a bounded flag wait gave up
+// (which = 1 stage-1 gate, 2 merge gate, >= 16 caller-chosen ids of esp_flag_wait; value = the awaited flag value);
+// code ESP_ERR_BAD_SLOT: stage 1 met a slot id outside the pool (which = 0, value = the id) and skipped that token.
 __device__ int g_decode_status[4];
 
 __device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
@@ -38,14 +41,14 @@ __device__ __forceinline__ uint4 ld_cg_v4(const void* p) {      // bypass L1: th
 }
 // One thread waits until *flag >= value (flags only ever grow).  Gives up after kGateLimitCycles, or at once
 // when an earlier wait on this device already failed; then records the failure and returns false.
-__device__ __noinline__ bool gate_wait(const int32_t* flag, int value, int which) {
+__device__ __noinline__ bool gate_wait(const int32_t* flag, int value, int which, int patience = 1) {
     if (ld_acquire_sys(flag) >= value) return true;
     const long long t0 = clock64();
     unsigned spins = 0;
     while (ld_acquire_sys(flag) < value) {
         if ((++spins & 255u) == 0) {
             if (*reinterpret_cast<volatile int*>(&g_decode_status[0]) != 0) return false;
-            if (clock64() - t0 > kGateLimitCycles) {
+            if (clock64() - t0 > *reinterpret_cast<volatile long long*>(&g_gate_limit_cycles) * patience) {
                 if (atomicCAS(&g_decode_status[0], 0, ESP_ERR_DEVICE_TIMEOUT) == 0) {
                     g_decode_status[1] = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
                     g_decode_status[2] = which;
@@ -65,7 +68,8 @@ __global__ void __launch_bounds__(kDecThreads) decode_stage1_kernel(
     int64_t v_stride_t, int64_t v_stride_h, const int32_t* __restrict__ req_to_tokens,
     int64_t rtt_stride, const int32_t* __restrict__ b_req_idx, const int32_t* __restrict__ b_seqlen,
     int batch, int num_q_heads, int group /* q heads per kv head */, int seq_block_size,
-    float scale_log2, const int32_t* __restrict__ wait_flag, int wait_value, const int32_t* __restrict__ value_base) {
+    float scale_log2, const int32_t* __restrict__ wait_flag, int wait_value, const int32_t* __restrict__ value_base,
+    int64_t pool_rows) {
     const int blk = blockIdx.x;
     const int hg = blockIdx.y;            // group of G consecutive q heads
     const int b = blockIdx.z;
@@ -122,7 +126,19 @@ __global__ void __launch_bounds__(kDecThreads) decode_stage1_kernel(
     for (int c0 = t0; c0 < t1; c0 += kDecChunk) {
         const int cn = min(kDecChunk, t1 - c0);
         __syncthreads();
-        for (int i = threadIdx.x; i < cn; i += kDecThreads) s_slots[i] = rtt[c0 + i];
+        for (int i = threadIdx.x; i < cn; i += kDecThreads) {
+            int32_t slot = rtt[c0 + i];
+            if (pool_rows > 0 && (slot < 0 || slot >= pool_rows)) {
+                // never dereferenced: the token is left out of the softmax and the id is reported
+                if (atomicCAS(&g_decode_status[0], 0, ESP_ERR_BAD_SLOT) == 0) {
+                    g_decode_status[1] = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+                    g_decode_status[2] = 0;
+                    g_decode_status[3] = slot;
+                }
+                slot = -1;
+            }
+            s_slots[i] = slot;
+        }
         __syncthreads();
         // each step covers 8 * kDecUnroll tokens of the chunk
         for (int base = 0; base < cn; base += 8 * kDecUnroll) {
@@ -131,8 +147,9 @@ __global__ void __launch_bounds__(kDecThreads) decode_stage1_kernel(
 #pragma unroll
             for (int u = 0; u < kDecUnroll; ++u) {
                 const int ti = base + u * 8 + slot_in_cta;
-                valid[u] = ti < cn;
-                const int64_t slot = s_slots[valid[u] ? ti : cn - 1];
+                int64_t slot = s_slots[ti < cn ? ti : cn - 1];
+                valid[u] = ti < cn && slot >= 0;
+                slot = slot >= 0 ? slot : 0;
                 kr[u] = ld_nc_v4(kbase + slot * k_stride_t);
                 vr[u] = ld_nc_v4(vbase + slot * v_stride_t);
             }
@@ -213,16 +230,17 @@ __global__ void __launch_bounds__(kDecThreads) decode_stage1_kernel(
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) M = fmaxf(M, s_red[w][g][128]);
+        const float Mu = (M == -INFINITY) ? 0.f : M;       // -inf only if every token of the block was skipped
         float L = 0.f, o = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float a = exp2f(s_red[w][g][128] - M);   // M is finite: the block has >= 1 token
+            const float a = exp2f(s_red[w][g][128] - Mu);
             L += s_red[w][g][129] * a;
             o += s_red[w][g][d] * a;
         }
         const int64_t row = ((int64_t)blk * batch + b) * num_q_heads + h0 + g;
-        mid_o[row * 128 + d] = o / L;
-        if (d == 0) mid_lse[row] = (M + log2f(L)) * kLn2;
+        mid_o[row * 128 + d] = L > 0.f ? o / L : 0.f;
+        if (d == 0) mid_lse[row] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
     }
 }
 
@@ -301,7 +319,7 @@ static int launch_stage1(float* mid_o, float* mid_lse, const void* q, const void
                          int64_t kst, int64_t ksh, int64_t vst, int64_t vsh, const int32_t* rtt,
                          int64_t rtt_stride, const int32_t* b_req_idx, const int32_t* b_seqlen,
                          int batch, int Hq, int Hkv, int max_len, int bs, float scale_log2,
-                         cudaStream_t s, const int32_t* wait_flag = nullptr, int wait_value = 0,
+                         cudaStream_t s, int64_t pool_rows, const int32_t* wait_flag = nullptr, int wait_value = 0,
                          const int32_t* value_base = nullptr) {
     const int group = Hq / Hkv;
     const int nblk = (max_len + bs - 1) / bs;
@@ -310,7 +328,7 @@ static int launch_stage1(float* mid_o, float* mid_lse, const void* q, const void
     dim3 grid(nblk, Hq / G, batch);
 #define ESP_S1(GG) decode_stage1_kernel<T, GG><<<grid, kDecThreads, 0, s>>>(mid_o, mid_lse, (const T*)q, \
         (const T*)k, (const T*)v, kst, ksh, vst, vsh, rtt, rtt_stride, b_req_idx, b_seqlen, batch, Hq, \
-        group, bs, scale_log2, wait_flag, wait_value, value_base)
+        group, bs, scale_log2, wait_flag, wait_value, value_base, pool_rows)
     switch (G) {
         case 8: ESP_S1(8); break;
         case 4: ESP_S1(4); break;
@@ -332,7 +350,7 @@ static int decode_stage1_impl(float* mid_o, float* mid_lse, const void* q, const
                                  int64_t req_to_tokens_stride, const int32_t* b_req_idx,
                                  const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
                                  int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
-                                 int32_t seq_block_size, int32_t dtype, float sm_scale, void* stream,
+                                 int32_t seq_block_size, int32_t dtype, float sm_scale, int64_t pool_rows, void* stream,
                                  const int32_t* wait_flag, int32_t wait_value, const int32_t* value_base = nullptr) {
     if (batch == 0 || max_len_in_batch <= 0) return ESP_OK;
     if (!mid_o || !mid_lse || !q || !k || !v || !req_to_tokens || !b_req_idx || !b_seqlen || batch < 0 ||
@@ -349,12 +367,12 @@ static int decode_stage1_impl(float* mid_o, float* mid_lse, const void* q, const
         return launch_stage1<__half>(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t,
                                      v_stride_h, req_to_tokens, req_to_tokens_stride, b_req_idx,
                                      b_seqlen, batch, num_q_heads, num_kv_heads, max_len_in_batch,
-                                     seq_block_size, scale, s, wait_flag, wait_value, value_base);
+                                     seq_block_size, scale, s, pool_rows, wait_flag, wait_value, value_base);
     if (dtype == ESP_DTYPE_BF16)
         return launch_stage1<__nv_bfloat16>(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t,
                                             v_stride_h, req_to_tokens, req_to_tokens_stride, b_req_idx,
                                             b_seqlen, batch, num_q_heads, num_kv_heads,
-                                            max_len_in_batch, seq_block_size, scale, s, wait_flag, wait_value, value_base);
+                                            max_len_in_batch, seq_block_size, scale, s, pool_rows, wait_flag, wait_value, value_base);
     return ESP_ERR_BAD_ARG;
 }
 
@@ -364,10 +382,10 @@ extern "C" int esp_decode_stage1(float* mid_o, float* mid_lse, const void* q, co
                                  int64_t req_to_tokens_stride, const int32_t* b_req_idx,
                                  const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
                                  int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
-                                 int32_t seq_block_size, int32_t dtype, float sm_scale, void* stream) {
+                                 int32_t seq_block_size, int32_t dtype, float sm_scale, int64_t pool_rows, void* stream) {
     return decode_stage1_impl(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t, v_stride_h, req_to_tokens,
                               req_to_tokens_stride, b_req_idx, b_seqlen, batch, num_q_heads, num_kv_heads, head_dim,
-                              max_len_in_batch, seq_block_size, dtype, sm_scale, stream, nullptr, 0);
+                              max_len_in_batch, seq_block_size, dtype, sm_scale, pool_rows, stream, nullptr, 0);
 }
 
 extern "C" int esp_decode_stage1_gated(float* mid_o, float* mid_lse, const void* q, const void* k,
@@ -376,12 +394,12 @@ extern "C" int esp_decode_stage1_gated(float* mid_o, float* mid_lse, const void*
                                        int64_t req_to_tokens_stride, const int32_t* b_req_idx,
                                        const int32_t* b_seqlen, int32_t batch, int32_t num_q_heads,
                                        int32_t num_kv_heads, int32_t head_dim, int32_t max_len_in_batch,
-                                       int32_t seq_block_size, int32_t dtype, float sm_scale,
+                                       int32_t seq_block_size, int32_t dtype, float sm_scale, int64_t pool_rows,
                                        const int32_t* wait_flag, int32_t wait_value, const int32_t* value_base, void* stream) {
     if (!wait_flag) return ESP_ERR_BAD_ARG;
     return decode_stage1_impl(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t, v_stride_h, req_to_tokens,
                               req_to_tokens_stride, b_req_idx, b_seqlen, batch, num_q_heads, num_kv_heads, head_dim,
-                              max_len_in_batch, seq_block_size, dtype, sm_scale, stream, wait_flag, wait_value, value_base);
+                              max_len_in_batch, seq_block_size, dtype, sm_scale, pool_rows, stream, wait_flag, wait_value, value_base);
 }
 
 static int decode_merge_impl(void* o, float* out_lse, const int32_t* b_seqlen, const float* mid_o,
@@ -452,9 +470,17 @@ __global__ void __launch_bounds__(1024) peer_push_kernel(const uint4* __restrict
     __syncthreads();
     if (threadIdx.x == 0) st_release_sys(tg.flag[blockIdx.x], value + (value_base ? *value_base : 0));
 }
+// After a wait on this device has timed out the kernels behind it returned without writing their results, so the
+// flag that would announce those results is not raised: the other side then times out too instead of reading garbage.
 __global__ void peer_signal_kernel(int32_t* flag, int value, const int32_t* __restrict__ value_base) {
+    if (*reinterpret_cast<volatile int*>(&g_decode_status[0]) == ESP_ERR_DEVICE_TIMEOUT) return;
     __threadfence_system();
     st_release_sys(flag, value + (value_base ? *value_base : 0));
+}
+// One thread waits (bounded) until *flag >= value.
+__global__ void flag_wait_kernel(const int32_t* flag, int value, const int32_t* __restrict__ value_base, int which,
+                                 int patience) {
+    gate_wait(flag, value + (value_base ? *value_base : 0), which, patience);
 }
 }  // namespace esp
 
@@ -515,6 +541,23 @@ extern "C" int esp_peer_signal(int32_t* remote_flag, int32_t value, const int32_
     return ESP_OK;
 }
 
+extern "C" int esp_flag_wait(const int32_t* flag, int32_t value, const int32_t* value_base, int32_t wait_id,
+                             int32_t patience, void* stream) {
+    if (!flag || wait_id < 16 || patience < 1 || patience > 1000) return ESP_ERR_BAD_ARG;
+    flag_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(flag, value, value_base, wait_id, patience);
+    ESP_LAUNCH_CHECK("flag_wait_kernel");
+    return ESP_OK;
+}
+
+namespace esp { int set_prefill_wait_limit(long long cycles); }
+
+extern "C" int esp_set_wait_limit_cycles(int64_t cycles) {
+    if (cycles <= 0) return ESP_ERR_BAD_ARG;
+    const long long v = cycles;
+    ESP_CUDA_TRY(cudaMemcpyToSymbol(g_gate_limit_cycles, &v, sizeof(v)));
+    return set_prefill_wait_limit(v);
+}
+
 extern "C" int esp_decode_device_status(int32_t out[4], int32_t clear) {
     if (!out) return ESP_ERR_BAD_ARG;
     ESP_CUDA_TRY(cudaDeviceSynchronize());
@@ -571,7 +614,7 @@ extern "C" int esp_decode_attention_noalloc(void* o, float* out_lse, const void*
                                             const int32_t* b_req_idx, const int32_t* b_seqlen,
                                             int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
                                             int32_t head_dim, int32_t max_len_in_batch, int32_t dtype,
-                                            int32_t o_dtype, float sm_scale, void* stream) {
+                                            int32_t o_dtype, float sm_scale, int64_t pool_rows, void* stream) {
     if (batch == 0) return ESP_OK;
     if (!o || !out_lse || !q || !k || !v || !req_to_tokens || !b_req_idx || !b_seqlen || batch < 0 ||
         num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads || max_len_in_batch < 0)
@@ -597,7 +640,7 @@ extern "C" int esp_decode_attention_noalloc(void* o, float* out_lse, const void*
     float* mid_lse = scratch + (long long)nblk * batch * num_q_heads * head_dim;
     rc = esp_decode_stage1(mid_o, mid_lse, q, k, v, k_stride_t, k_stride_h, v_stride_t, v_stride_h, req_to_tokens,
                            req_to_tokens_stride, b_req_idx, b_seqlen, batch, num_q_heads, num_kv_heads, head_dim,
-                           max_len, (int32_t)bs, dtype, sm_scale, stream);
+                           max_len, (int32_t)bs, dtype, sm_scale, pool_rows, stream);
     if (rc) return rc;
     return esp_decode_merge(o, out_lse, b_seqlen, mid_o, mid_lse, batch, num_q_heads, head_dim, nblk, (int32_t)bs,
                             o_dtype, stream);

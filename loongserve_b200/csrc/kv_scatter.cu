@@ -13,6 +13,20 @@ char* last_cuda_error_buf() {
     return buf;
 }
 
+// Slot ids that fall outside the pool are never dereferenced: the row is skipped and the first such id of a run is
+// recorded here as {ESP_ERR_BAD_SLOT, kernel id, position of the id in its index array, the id clamped to int32}.
+__device__ int g_kv_status[4];
+
+__device__ __forceinline__ bool slot_ok(int64_t slot, int64_t pool_rows, int kernel_id, int64_t pos) {
+    if (pool_rows <= 0 || (slot >= 0 && slot < pool_rows)) return true;      // pool_rows <= 0: caller opted out
+    if (threadIdx.x == 0 && atomicCAS(&g_kv_status[0], 0, ESP_ERR_BAD_SLOT) == 0) {
+        g_kv_status[1] = kernel_id;
+        g_kv_status[2] = (int)(pos > 2147483647LL ? 2147483647LL : pos);
+        g_kv_status[3] = (int)(slot > 2147483647LL ? 2147483647LL : (slot < -2147483647LL ? -2147483647LL : slot));
+    }
+    return false;
+}
+
 template <bool IDX64>
 __device__ __forceinline__ int64_t load_idx(const void* p, int64_t i) {
     if (IDX64) return reinterpret_cast<const int64_t*>(p)[i];
@@ -54,9 +68,10 @@ template <bool IDX64>
 __global__ void __launch_bounds__(256) kv_scatter_kernel(
     const char* __restrict__ src, int64_t src_row_b, int64_t src_head_b, char* __restrict__ out,
     int64_t out_row_b, int64_t out_head_b, const void* __restrict__ dest, int64_t n, int heads2,
-    int head_bytes) {
+    int head_bytes, int64_t pool_rows) {
     for (int64_t i = blockIdx.x; i < n; i += gridDim.x) {
         const int64_t d = load_idx<IDX64>(dest, i);
+        if (!slot_ok(d, pool_rows, 1, i)) continue;
         copy_row(src + i * src_row_b, src_head_b, out + d * out_row_b, out_head_b, heads2, head_bytes);
     }
 }
@@ -84,7 +99,7 @@ __global__ void __launch_bounds__(256) kv_scatter_register_kernel(
     const void* __restrict__ mem_index, char* __restrict__ pool, int64_t pool_row_b,
     int64_t pool_head_b, int32_t* __restrict__ req_to_token, int64_t rtt_stride,
     const int32_t* __restrict__ b_req_idx, int64_t num_used, int row_cap, int should_register,
-    int heads2, int head_bytes) {
+    int heads2, int head_bytes, int64_t pool_rows) {
     const int b = blockIdx.y;
     int n_new = new_len[b];
     const int rb = range_begin[b], re = range_end[b];
@@ -96,6 +111,7 @@ __global__ void __launch_bounds__(256) kv_scatter_register_kernel(
     if (should_register) rtt = req_to_token + (int64_t)b_req_idx[b] * rtt_stride + cur_kv_cache_index[b];
     for (int n = blockIdx.x; n < n_new; n += gridDim.x) {
         const int64_t slot = load_idx<IDX64>(mem_index, base + n);
+        if (!slot_ok(slot, pool_rows, 2, base + n)) continue;
         copy_row(kv + (src0 + n) * kv_row_b, kv_head_b, pool + slot * pool_row_b, pool_head_b, heads2,
                  head_bytes);
         if (should_register && threadIdx.x == 0) rtt[n] = (int32_t)slot;
@@ -139,7 +155,7 @@ __global__ void __launch_bounds__(256) mig_gather_kernel(
     int64_t rtt_stride, int32_t* __restrict__ mem_state, const char* __restrict__ kv_cache,
     int64_t kv_layer_b, int64_t kv_row_b, const int32_t* __restrict__ request_ids,
     const int32_t* __restrict__ num_tokens, const int64_t* __restrict__ cumsum,
-    const int32_t* __restrict__ b_seq_len, int row_bytes) {
+    const int32_t* __restrict__ b_seq_len, int row_bytes, int64_t pool_rows) {
     const int b = blockIdx.y, layer = blockIdx.z;
     const int n = num_tokens[b];
     const int L = b_seq_len[b];
@@ -147,6 +163,7 @@ __global__ void __launch_bounds__(256) mig_gather_kernel(
     const int32_t* rtt = req_to_token + (int64_t)request_ids[b] * rtt_stride + (L - n);
     for (int i = blockIdx.x; i < n; i += gridDim.x) {
         const int64_t slot = rtt[i];
+        if (!slot_ok(slot, pool_rows, 3, off + i)) continue;
         if (layer == 0 && threadIdx.x == 0) mem_state[slot] = 0;
         copy_row(kv_cache + layer * kv_layer_b + slot * kv_row_b, 0,
                  send_buf + ((int64_t)layer * total_tokens + off + i) * row_bytes, 0, 1, row_bytes);
@@ -159,7 +176,7 @@ __global__ void __launch_bounds__(256) mig_scatter_kernel(
     int64_t rtt_stride, char* __restrict__ kv_cache, int64_t kv_layer_b, int64_t kv_row_b,
     const void* __restrict__ alloc_mem, const int32_t* __restrict__ request_ids,
     const int32_t* __restrict__ num_tokens, const int64_t* __restrict__ cumsum,
-    const int32_t* __restrict__ b_seq_len, int row_bytes) {
+    const int32_t* __restrict__ b_seq_len, int row_bytes, int64_t pool_rows) {
     const int b = blockIdx.y, layer = blockIdx.z;
     const int n = num_tokens[b];
     const int L = b_seq_len[b];
@@ -167,6 +184,7 @@ __global__ void __launch_bounds__(256) mig_scatter_kernel(
     int32_t* rtt = req_to_token + (int64_t)request_ids[b] * rtt_stride + L;
     for (int i = blockIdx.x; i < n; i += gridDim.x) {
         const int64_t slot = load_idx<IDX64>(alloc_mem, off + i);
+        if (!slot_ok(slot, pool_rows, 4, off + i)) continue;
         if (layer == 0 && threadIdx.x == 0) rtt[i] = (int32_t)slot;
         copy_row(recv_buf + ((int64_t)layer * total_tokens + off + i) * row_bytes, 0,
                  kv_cache + layer * kv_layer_b + slot * kv_row_b, 0, 1, row_bytes);
@@ -201,6 +219,7 @@ extern "C" const char* esp_strerror(int code) {
         case ESP_ERR_UNSUPPORTED: return "unsupported configuration";
         case ESP_ERR_NCCL: return "NCCL call failed";
         case ESP_ERR_TOO_LARGE: return "size beyond the entry point's fixed capacity";
+        case ESP_ERR_BAD_SLOT: return "slot id outside the pool (row skipped)";
         default: return "unknown error";
     }
 }
@@ -211,7 +230,7 @@ extern "C" int esp_abi_version(void) { return ESP_ABI_VERSION; }
 extern "C" int esp_kv_scatter(const void* src, int64_t src_row_stride, int64_t src_head_stride,
                               void* out, int64_t out_row_stride, int64_t out_head_stride,
                               const void* dest, int32_t idx64, int64_t n, int32_t heads2,
-                              int32_t head_dim, int32_t elem_bytes, void* stream) {
+                              int32_t head_dim, int32_t elem_bytes, int64_t pool_rows, void* stream) {
     if (n == 0) return ESP_OK;
     if (!src || !out || !dest || n < 0) return ESP_ERR_BAD_ARG;
     int rc = check_rows(heads2, head_dim, elem_bytes, src_row_stride, src_head_stride, out_row_stride,
@@ -224,11 +243,11 @@ extern "C" int esp_kv_scatter(const void* src, int64_t src_row_stride, int64_t s
     if (idx64)
         kv_scatter_kernel<true><<<row_grid(n), 256, 0, s>>>(sp, src_row_stride * elem_bytes,
             src_head_stride * elem_bytes, op, out_row_stride * elem_bytes, out_head_stride * elem_bytes,
-            dest, n, heads2, hb);
+            dest, n, heads2, hb, pool_rows);
     else
         kv_scatter_kernel<false><<<row_grid(n), 256, 0, s>>>(sp, src_row_stride * elem_bytes,
             src_head_stride * elem_bytes, op, out_row_stride * elem_bytes, out_head_stride * elem_bytes,
-            dest, n, heads2, hb);
+            dest, n, heads2, hb, pool_rows);
     ESP_LAUNCH_CHECK("kv_scatter_kernel");
     return ESP_OK;
 }
@@ -254,7 +273,7 @@ extern "C" int esp_kv_scatter_register(
     int32_t idx64, void* pool, int64_t pool_row_stride, int64_t pool_head_stride,
     int32_t* req_to_token, int64_t req_to_token_stride, const int32_t* b_req_idx,
     int64_t num_used_mem_index, int32_t max_len_in_batch, int32_t should_register, int32_t heads2,
-    int32_t head_dim, int32_t elem_bytes, void* stream) {
+    int32_t head_dim, int32_t elem_bytes, int64_t pool_rows, void* stream) {
     if (batch == 0 || max_len_in_batch <= 0) return ESP_OK;
     if (!new_len || !range_begin || !range_end || !new_len_cumsum || !kv || !kv_b_start_loc ||
         !mem_index || !pool || batch < 0)
@@ -278,7 +297,7 @@ extern "C" int esp_kv_scatter_register(
         kv_row_stride * elem_bytes, kv_head_stride * elem_bytes, kv_b_start_loc, cur_kv_cache_index,   \
         mem_index, (char*)pool, pool_row_stride * elem_bytes, pool_head_stride * elem_bytes,           \
         req_to_token, req_to_token_stride, b_req_idx, num_used_mem_index, row_cap, should_register,    \
-        heads2, hb
+        heads2, hb, pool_rows
     if (idx64) kv_scatter_register_kernel<true><<<grid, 256, 0, s>>>(ESP_SR_ARGS);
     else kv_scatter_register_kernel<false><<<grid, 256, 0, s>>>(ESP_SR_ARGS);
 #undef ESP_SR_ARGS
@@ -333,7 +352,7 @@ extern "C" int esp_mig_gather(void* send_buf, int64_t total_tokens, const int32_
                               const int32_t* request_ids, const int32_t* num_tokens,
                               const int64_t* num_tokens_cumsum, const int32_t* b_seq_len,
                               int32_t batch, int32_t max_num_tokens, int32_t num_layers,
-                              int32_t heads2, int32_t head_dim, int32_t elem_bytes, void* stream) {
+                              int32_t heads2, int32_t head_dim, int32_t elem_bytes, int64_t pool_rows, void* stream) {
     if (batch == 0 || total_tokens == 0 || max_num_tokens <= 0) return ESP_OK;
     if (!send_buf || !req_to_token || !mem_state || !kv_cache || !request_ids || !num_tokens ||
         !num_tokens_cumsum || !b_seq_len || batch < 0 || num_layers <= 0)
@@ -347,7 +366,7 @@ extern "C" int esp_mig_gather(void* send_buf, int64_t total_tokens, const int32_
     mig_gather_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
         (char*)send_buf, total_tokens, req_to_token, req_to_token_stride, mem_state,
         (const char*)kv_cache, kv_layer_stride * elem_bytes, kv_row_stride * elem_bytes, request_ids,
-        num_tokens, num_tokens_cumsum, b_seq_len, heads2 * head_dim * elem_bytes);
+        num_tokens, num_tokens_cumsum, b_seq_len, heads2 * head_dim * elem_bytes, pool_rows);
     ESP_LAUNCH_CHECK("mig_gather_kernel");
     return ESP_OK;
 }
@@ -358,7 +377,7 @@ extern "C" int esp_mig_scatter(const void* recv_buf, int64_t total_tokens, int32
                                const int32_t* request_ids, const int32_t* num_tokens,
                                const int64_t* num_tokens_cumsum, const int32_t* b_seq_len,
                                int32_t batch, int32_t max_num_tokens, int32_t num_layers,
-                               int32_t heads2, int32_t head_dim, int32_t elem_bytes, void* stream) {
+                               int32_t heads2, int32_t head_dim, int32_t elem_bytes, int64_t pool_rows, void* stream) {
     if (batch == 0 || total_tokens == 0 || max_num_tokens <= 0) return ESP_OK;
     if (!recv_buf || !req_to_token || !kv_cache || !alloc_mem || !request_ids || !num_tokens ||
         !num_tokens_cumsum || !b_seq_len || batch < 0 || num_layers <= 0)
@@ -373,11 +392,29 @@ extern "C" int esp_mig_scatter(const void* recv_buf, int64_t total_tokens, int32
     const int rowb = heads2 * head_dim * elem_bytes;
     if (idx64) mig_scatter_kernel<true><<<grid, 256, 0, s>>>((const char*)recv_buf, total_tokens,
         req_to_token, req_to_token_stride, (char*)kv_cache, kv_layer_stride * elem_bytes,
-        kv_row_stride * elem_bytes, alloc_mem, request_ids, num_tokens, num_tokens_cumsum, b_seq_len, rowb);
+        kv_row_stride * elem_bytes, alloc_mem, request_ids, num_tokens, num_tokens_cumsum, b_seq_len, rowb, pool_rows);
     else mig_scatter_kernel<false><<<grid, 256, 0, s>>>((const char*)recv_buf, total_tokens,
         req_to_token, req_to_token_stride, (char*)kv_cache, kv_layer_stride * elem_bytes,
-        kv_row_stride * elem_bytes, alloc_mem, request_ids, num_tokens, num_tokens_cumsum, b_seq_len, rowb);
+        kv_row_stride * elem_bytes, alloc_mem, request_ids, num_tokens, num_tokens_cumsum, b_seq_len, rowb, pool_rows);
     ESP_LAUNCH_CHECK("mig_scatter_kernel");
+    return ESP_OK;
+}
+
+extern "C" int esp_kv_device_status(int32_t out[4], int32_t clear) {
+    if (!out) return ESP_ERR_BAD_ARG;
+    ESP_CUDA_TRY(cudaDeviceSynchronize());
+    ESP_CUDA_TRY(cudaMemcpyFromSymbol(out, g_kv_status, sizeof(int) * 4));
+    if (clear) {
+        int zero[4] = {0, 0, 0, 0};
+        ESP_CUDA_TRY(cudaMemcpyToSymbol(g_kv_status, zero, sizeof(zero)));
+    }
+    return ESP_OK;
+}
+
+extern "C" int esp_memcpy_async(void* dst, const void* src, int64_t bytes, void* stream) {
+    if (bytes == 0) return ESP_OK;
+    if (!dst || !src || bytes < 0) return ESP_ERR_BAD_ARG;
+    ESP_CUDA_TRY(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, (cudaStream_t)stream));
     return ESP_OK;
 }
 

@@ -42,8 +42,18 @@ constexpr int kPolyPer32 = ESP_POLY_EXP_PER_32;
 static_assert(kPolyPer32 == 0 || kPolyPer32 == 2 || kPolyPer32 == 4 || kPolyPer32 == 8 || kPolyPer32 == 16 || kPolyPer32 == 32,
               "ESP_POLY_EXP_PER_32 must be 0 or a power of two up to 32");
 constexpr int TMEM_COLS = 512;
-constexpr long long kWaitLimitCycles = 2000000000LL;   // about a second
 constexpr float kRescaleThreshold = 8.0f;              // lazy O rescale: tolerate 2^8 growth
+#ifndef ESP_SPEC_MAX
+#define ESP_SPEC_MAX 0
+#endif
+constexpr bool kSpeculateMax = ESP_SPEC_MAX != 0;
+#ifndef ESP_CHEAP_DESC
+#define ESP_CHEAP_DESC 0
+#endif
+#ifndef ESP_WARP_ARRIVE
+#define ESP_WARP_ARRIVE 0
+#endif
+constexpr int kPReadyArrivals = ESP_WARP_ARRIVE ? 4 : 128;   // arrivals that publish one tile's P
 
 enum BarIdx { B_QFULL = 0, B_KVFULL = 2, B_KVEMPTY = 2 + NSTAGE, B_SFULL = 2 + 2 * NSTAGE,
               B_PREADY = 4 + 2 * NSTAGE, B_ODONE = 6 + 2 * NSTAGE, B_COUNT = 8 + 2 * NSTAGE };
@@ -56,6 +66,8 @@ constexpr int SMEM_TOTAL = SMEM_MISC + 16;
 constexpr int SMEM_DYN = SMEM_TOTAL + 1024;            // slack to align the base to 1024 B
 
 __device__ int g_esp_status[4];
+// Bound of every mbarrier wait in SM cycles (about a second by default); esp_set_wait_limit_cycles changes it.
+__device__ long long g_wait_limit_cycles = 2000000000LL;
 
 #ifdef ESP_PREFILL_TRACE
 // Tuning aid, compiled only into experiment builds: per-phase SM clock stamps of one CTA.
@@ -84,20 +96,12 @@ __device__ __noinline__ void report_timeout(int which, int detail) {
 }
 
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* s_abort, int which, int detail) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 63u) == 0) {
-            if (*s_abort) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
-                report_timeout(which, detail);
-                *s_abort = 1;
-                return false;
-            }
-        }
+    const int r = mbar_wait_bounded(bar, parity, &g_wait_limit_cycles, s_abort);
+    if (r == 2) {
+        report_timeout(which, detail);
+        *s_abort = 1;
     }
-    return true;
+    return r == 0;
 }
 
 template <typename T> struct Fmt;
@@ -205,8 +209,9 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
 #endif
 // p = 2^(s*scale - m) for one 32-column chunk; packs to 16-bit pairs and returns the chunk's row sum
 // (two independent packed accumulators)
-template <typename T, int OFF>
-__device__ __forceinline__ float chunk_exp(const uint32_t (&r)[32], float scale, float neg_m, uint32_t (&pk)[32]) {
+template <typename T, int OFF, bool kTrackMax = false>
+__device__ __forceinline__ float chunk_exp(const uint32_t (&r)[32], float scale, float neg_m, uint32_t (&pk)[32],
+                                           float* mx4 = nullptr) {
     const float2 sc2 = make_float2(scale, scale), nm2 = make_float2(neg_m, neg_m);
     float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
     constexpr int kStride = kPolyPer32 > 0 ? 32 / kPolyPer32 : 1;   // every kStride-th pair goes to the FMA pipe
@@ -238,6 +243,7 @@ __device__ __forceinline__ float chunk_exp(const uint32_t (&r)[32], float scale,
         }
         acc[(i / 2) & 1] = __fadd2_rn(acc[(i / 2) & 1], e);
         pk[OFF + i / 2] = Cvt<T>::pack(e.x, e.y);
+        if (kTrackMax) mx4[(i / 2) & 3] = fmax3(mx4[(i / 2) & 3], __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
     }
 #endif
     const float2 t = __fadd2_rn(acc[0], acc[1]);
@@ -292,7 +298,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
     if (threadIdx.x == 0) {
         *s_abort = 0;
         *s_skip = (*reinterpret_cast<volatile int*>(&g_esp_status[0]) != 0);
-        for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i >= B_PREADY && i < B_PREADY + QT) ? BM : 1);
+        for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i >= B_PREADY && i < B_PREADY + QT) ? kPReadyArrivals : 1);
         fence_barrier_init();
     }
     if (warp == 8 && lane == 0) {
@@ -340,6 +346,31 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_s = make_idesc(Fmt<T>::kAB, 0, BM, BN);
         constexpr uint32_t idesc_pv = make_idesc(Fmt<T>::kAB, 1, BM, HD);
+#if ESP_CHEAP_DESC
+        // The issuing thread shares its scheduler with two softmax warps, so every instruction between two MMAs costs
+        // tensor-pipe time: descriptors are formed once per operand tile and stepped with one 64-bit add per MMA
+        // (the address field cannot carry out of its 14 bits: shared memory ends below 256 KiB).
+        const uint64_t dq0 = desc_kmajor_sw128(smem_base + SMEM_Q);
+        const uint64_t dk0 = desc_kmajor_sw128(smem_base + SMEM_KV);
+        const uint64_t dv0 = desc_mnmajor_sw128(smem_base + SMEM_KV, HALF_BYTES);
+        auto issue_s = [&](int t, int stage) {
+            const uint64_t qa = dq0 + (uint64_t)(t * (TILE_BYTES >> 4));
+            const uint64_t kb = dk0 + (uint64_t)(stage * (TILE_BYTES >> 4));
+            const uint32_t d = tmem_base + t * BN;
+#pragma unroll
+            for (int k = 0; k < HD / 16; ++k) {
+                const uint64_t off = (uint64_t)(((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4);
+                umma_ss(d, qa + off, kb + off, idesc_s, k > 0);
+            }
+        };
+        auto issue_pv = [&](int t, int stage, bool acc) {
+            const uint64_t vb = dv0 + (uint64_t)(stage * (TILE_BYTES >> 4));
+            const uint32_t d = tmem_base + QT * BN + t * HD, a = tmem_base + t * BN;
+#pragma unroll
+            for (int k = 0; k < BN / 16; ++k)
+                umma_ts(d, a + k * 8, vb + (uint64_t)(k * (2048 >> 4)), idesc_pv, (acc || k > 0) ? 1u : 0u);
+        };
+#else
         auto issue_s = [&](int t, int stage) {
             const uint32_t qa = smem_base + SMEM_Q + t * TILE_BYTES;
             const uint32_t kb = smem_base + SMEM_KV + stage * TILE_BYTES;
@@ -357,6 +388,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                         desc_mnmajor_sw128(vb + k * 2048, HALF_BYTES), idesc_pv, (acc || k > 0) ? 1u : 0u);
             }
         };
+#endif
         bool ok = true;
 #pragma unroll
         for (int t = 0; t < QT; ++t)
@@ -457,52 +489,89 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                 const int r0 = m0 + t * BM;
                 const bool masked = (n0 + BN - 1 > r0 - delta) || (n0 + BN > kv_len);
                 const int limit = min(row - delta, kv_len - 1) - n0;     // columns <= limit are visible
-                float mx = fmaxf(chunk_max(sr[0], 0, limit, masked), chunk_max(sr[1], 32, limit, masked));
-                tmem_wait_ld();
-                mx = fmax3(mx, chunk_max(sr[2], 64, limit, masked), chunk_max(sr[3], 96, limit, masked));
-                ESP_TRACE(t, j, 3);
-                const float m_tile = mx * scale;
-                const float m_new = fmaxf(m_run, m_tile);
-                // lazy rescale: keep the old reference maximum unless the row maximum grew by > 2^8
-                const bool need = (m_new > m_run + kRescaleThreshold) || (m_run == -INFINITY && m_new > -INFINITY);
-                float alpha = 1.f;
-                if (need) {
-                    alpha = ex2(m_run - m_new);       // 0 when the row had no key before
-                    l_run *= alpha;
-                    m_run = m_new;
-                }
-                if (j > 0 && __any_sync(0xffffffffu, need)) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t orow[32];
-                        tmem_ld32(tO + c * 32, orow);
+                // After the first tile the running maximum rarely grows by more than the lazy-rescale threshold, so the
+                // exponentials of an unmasked tile are taken against the running maximum straight away while the
+                // tile's own maximum is found alongside on the ALU pipe.  P is stored only once every row of the warp
+                // is known to have stayed within the threshold; otherwise S (still intact in tensor memory) is read
+                // again and the tile is done the slow way: maximum first, O rescaled, then the exponentials.
+                float lsum = 0.f;
+                bool published = false;
+                if (kSpeculateMax && !masked && j > 0) {
+                    ESP_TRACE(t, j, 3);
+                    const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    uint32_t pa[32], pb[32];
+                    const float s0 = chunk_exp<T, 0, true>(sr[0], scale, neg_m, pa, mx4);
+                    const float s1 = chunk_exp<T, 16, true>(sr[1], scale, neg_m, pa, mx4);
+                    tmem_wait_ld();
+                    const float s2 = chunk_exp<T, 0, true>(sr[2], scale, neg_m, pb, mx4);
+                    const float s3 = chunk_exp<T, 16, true>(sr[3], scale, neg_m, pb, mx4);
+                    const float m_tile = fmaxf(fmax3(mx4[0], mx4[1], mx4[2]), mx4[3]) * scale;
+                    const bool outgrown = (m_tile > m_run + kRescaleThreshold) || (m_run == -INFINITY);
+                    if (!__any_sync(0xffffffffu, outgrown)) {
+                        tmem_st32(tS, pa);
+                        tmem_st32(tS + 32, pb);
+                        lsum = (s0 + s1) + (s2 + s3);
+                        published = true;
+                    } else {
+                        tmem_ld32(tS, sr[0]);
+                        tmem_ld32(tS + 32, sr[1]);
                         tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
-                        tmem_st32(tO + c * 32, orow);
+                        tmem_ld32(tS + 64, sr[2]);
+                        tmem_ld32(tS + 96, sr[3]);
                     }
                 }
-                const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
-                float lsum;
-                {
-                    uint32_t pk[32];
-                    const float s0 = chunk_exp<T, 0>(sr[0], scale, neg_m, pk);
-                    const float s1 = chunk_exp<T, 16>(sr[1], scale, neg_m, pk);
-                    tmem_st32(tS, pk);                 // P aliases the first 64 columns of S
-                    lsum = s0 + s1;
-                }
-                {
-                    uint32_t pk[32];
-                    const float s2 = chunk_exp<T, 0>(sr[2], scale, neg_m, pk);
-                    const float s3 = chunk_exp<T, 16>(sr[3], scale, neg_m, pk);
-                    tmem_st32(tS + 32, pk);
-                    lsum += s2 + s3;
+                if (!published) {
+                    float mx = fmaxf(chunk_max(sr[0], 0, limit, masked), chunk_max(sr[1], 32, limit, masked));
+                    tmem_wait_ld();
+                    mx = fmax3(mx, chunk_max(sr[2], 64, limit, masked), chunk_max(sr[3], 96, limit, masked));
+                    ESP_TRACE(t, j, 3);
+                    const float m_new = fmaxf(m_run, mx * scale);
+                    // lazy rescale: keep the old reference maximum unless the row maximum grew by > 2^8
+                    const bool need = (m_new > m_run + kRescaleThreshold) || (m_run == -INFINITY && m_new > -INFINITY);
+                    float alpha = 1.f;
+                    if (need) {
+                        alpha = ex2(m_run - m_new);       // 0 when the row had no key before
+                        l_run *= alpha;
+                        m_run = m_new;
+                    }
+                    if (j > 0 && __any_sync(0xffffffffu, need)) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t orow[32];
+                            tmem_ld32(tO + c * 32, orow);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                            tmem_st32(tO + c * 32, orow);
+                        }
+                    }
+                    const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+                    {
+                        uint32_t pk[32];
+                        const float s0 = chunk_exp<T, 0>(sr[0], scale, neg_m, pk);
+                        const float s1 = chunk_exp<T, 16>(sr[1], scale, neg_m, pk);
+                        tmem_st32(tS, pk);                 // P aliases the first 64 columns of S
+                        lsum = s0 + s1;
+                    }
+                    {
+                        uint32_t pk[32];
+                        const float s2 = chunk_exp<T, 0>(sr[2], scale, neg_m, pk);
+                        const float s3 = chunk_exp<T, 16>(sr[3], scale, neg_m, pk);
+                        tmem_st32(tS + 32, pk);
+                        lsum += s2 + s3;
+                    }
                 }
                 ESP_TRACE(t, j, 4);
                 l_run += lsum;
                 tmem_wait_st();
                 tc_fence_before();
+#if ESP_WARP_ARRIVE
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_PREADY + t));
+#else
                 mbar_arrive(bar(B_PREADY + t));
+#endif
                 ESP_TRACE(t, j, 5);
             }
             if (ok) {
@@ -625,6 +694,11 @@ __global__ void state_init_kernel(float* m, float* l, int64_t n) {
 __global__ void lse_kernel(const float* m, const float* l, float* lse, int64_t n) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         lse[i] = l[i] > 0.f ? m[i] * 0.6931471805599453f + logf(l[i]) : -INFINITY;
+}
+
+int set_prefill_wait_limit(long long cycles) {
+    ESP_CUDA_TRY(cudaMemcpyToSymbol(g_wait_limit_cycles, &cycles, sizeof(cycles)));
+    return ESP_OK;
 }
 
 }  // namespace esp

@@ -44,6 +44,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Wait for a phase of an mbarrier for at most *limit_cycles SM cycles (read only once the wait is already long).
+// Returns 0 when the phase completed, 1 when *abort became non-zero meanwhile, 2 when the limit ran out.
+__device__ __forceinline__ int mbar_wait_bounded(uint32_t bar, uint32_t parity, const long long* limit_cycles,
+                                                 volatile int* abort) {
+    if (mbar_try_wait(bar, parity)) return 0;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0) {
+            if (abort != nullptr && *abort) return 1;
+            if (clock64() - t0 > *reinterpret_cast<const volatile long long*>(limit_cycles)) return 2;
+        }
+    }
+    return 0;
+}
+
 // ---------------------------------------------------------------- TMA (tiled, 3-D, this CTA's smem)
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");

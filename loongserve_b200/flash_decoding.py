@@ -28,7 +28,7 @@ def flash_decoding_stage1(mid_o, mid_o_logexpsum, q, k, v, req_to_tokens, b_req_
         ptr(mid_o), ptr(mid_o_logexpsum), ptr(q), ptr(k), ptr(v), k.stride(0), k.stride(1), v.stride(0),
         v.stride(1), ptr(req_to_tokens), req_to_tokens.stride(0), ptr(b_req_idx), ptr(b_seqlen),
         q.shape[0], q.shape[1], k.shape[1], q.shape[2], int(max_len_in_batch), int(seq_block_size),
-        dtype_tag(q), float(sm_scale), stream_ptr())
+        dtype_tag(q), float(sm_scale), min(k.shape[0], v.shape[0]), stream_ptr())
     _lib.check(rc, "esp_decode_stage1")
 
 
@@ -70,3 +70,18 @@ def longserve_token_decode_attention_flash_decoding(q, req_to_token_indexs, b_re
                                   max_len_in_batch, mid_o, mid_o_logexpsum, BLOCK_SEQ)
     longserve_flash_decode_stage2(mid_o, mid_o_logexpsum, b_seq_len, o_tensor.view(shape), out_lse, BLOCK_SEQ)
     return o_tensor, out_lse
+
+
+def device_status(clear: bool = True):
+    """(code, block, which, value) of the decode kernels and flag waits on the current device: code 0, or
+    ESP_ERR_DEVICE_TIMEOUT (-4) for a flag wait that ran out, or ESP_ERR_BAD_SLOT (-8) for a slot id outside the pool
+    (that token was left out).  Synchronises the device."""
+    import ctypes as C
+    buf = (C.c_int32 * 4)()
+    _lib.check(_lib.attn().esp_decode_device_status(buf, 1 if clear else 0), "esp_decode_device_status")
+    return tuple(buf)
+
+
+def set_wait_limit_cycles(cycles: int):
+    """Limit of every bounded in-kernel wait on the current device, in SM cycles (default 2e9, about a second)."""
+    _lib.check(_lib.attn().esp_set_wait_limit_cycles(int(cycles)), "esp_set_wait_limit_cycles")

@@ -20,7 +20,8 @@ def destindex_copy_kv(K, DestLoc, Out):
     heads, dim, eb = _rows(K)
     assert Out.shape[1] == heads and Out.shape[2] == dim and Out.dtype == K.dtype and DestLoc.is_contiguous()
     rc = _lib.attn().esp_kv_scatter(ptr(K), K.stride(0), K.stride(1), ptr(Out), Out.stride(0), Out.stride(1),
-                                    ptr(DestLoc), idx64_flag(DestLoc), DestLoc.shape[0], heads, dim, eb, stream_ptr())
+                                    ptr(DestLoc), idx64_flag(DestLoc), DestLoc.shape[0], heads, dim, eb, Out.shape[0],
+                                    stream_ptr())
     _lib.check(rc, "esp_kv_scatter")
 
 
@@ -58,7 +59,7 @@ def destindex_copy_and_register_kv(batch_size, new_kv_cache_len, kv_range_begin,
         ptr(kv), kv.stride(0), kv.stride(1), ptr(kv_b_start_loc), ptr(cur_kv_cache_index), ptr(mem_index),
         idx64_flag(mem_index), ptr(total_kv_cache), total_kv_cache.stride(0), total_kv_cache.stride(1),
         ptr(req_to_token_indexs), req_to_token_indexs.stride(0), ptr(b_req_idx), int(num_used_mem_index),
-        int(max_len_in_batch), 1 if should_register_kv else 0, heads, dim, eb, stream_ptr())
+        int(max_len_in_batch), 1 if should_register_kv else 0, heads, dim, eb, total_kv_cache.shape[0], stream_ptr())
     _lib.check(rc, "esp_kv_scatter_register")
 
 
@@ -112,7 +113,7 @@ def decoding_stage_migration_sender_kernel(send_buf, req_to_token_indexes, mem_s
                                     req_to_token_indexes.stride(0), ptr(mem_state), ptr(kv_cache), kv_cache.stride(0),
                                     kv_cache.stride(1), ptr(request_ids), ptr(num_tokens), ptr(cumsum), ptr(b_seq_len),
                                     request_ids.shape[0], mx, kv_cache.shape[0], kv_cache.shape[2], kv_cache.shape[3],
-                                    kv_cache.element_size(), stream_ptr())
+                                    kv_cache.element_size(), kv_cache.shape[1], stream_ptr())
     _lib.check(rc, "esp_mig_gather")
 
 
@@ -129,5 +130,14 @@ def decoding_stage_migration_receiver_kernel(recv_buf, req_to_token_indexes, kv_
                                      kv_cache.stride(1), ptr(alloc_mem), idx64_flag(alloc_mem), ptr(request_ids),
                                      ptr(num_tokens), ptr(cumsum), ptr(b_seq_len), request_ids.shape[0], mx,
                                      kv_cache.shape[0], kv_cache.shape[2], kv_cache.shape[3], kv_cache.element_size(),
-                                     stream_ptr())
+                                     kv_cache.shape[1], stream_ptr())
     _lib.check(rc, "esp_mig_scatter")
+
+
+def device_status(clear: bool = True):
+    """(code, kernel, position, slot id) of the slot-id checks of the pool kernels on the current device; code 0 = every
+    id seen so far was inside its pool.  Synchronises the device."""
+    import ctypes as C
+    buf = (C.c_int32 * 4)()
+    _lib.check(_lib.attn().esp_kv_device_status(buf, 1 if clear else 0), "esp_kv_device_status")
+    return tuple(buf)

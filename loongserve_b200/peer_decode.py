@@ -100,7 +100,8 @@ class FusedDecodeGroup:
         _lib.check(lib.esp_decode_stage1(ptr(mid_o), ptr(mid_lse), ptr(q), ptr(k_cache), ptr(v_cache), k_cache.stride(0),
                                          k_cache.stride(1), v_cache.stride(0), v_cache.stride(1), ptr(req_to_token_indexs),
                                          req_to_token_indexs.stride(0), ptr(b_req_idx), ptr(b_seq_len), batch, Hq, Hkv, D,
-                                         max_len_in_batch, block_seq, dtype_tag(pool_layer), 0.0, s), "esp_decode_stage1")
+                                         max_len_in_batch, block_seq, dtype_tag(pool_layer), 0.0, pool_layer.shape[0], s),
+                   "esp_decode_stage1")
         # merge own blocks into slot [master] of the partial region, then merge the P slots
         own_o = self.base + self.off_o + self.master * batch * Hq * D * 4
         own_lse = self.base + self.off_lse + self.master * batch * Hq * 4
@@ -131,8 +132,8 @@ class FusedDecodeGroup:
         _lib.check(lib.esp_decode_stage1_gated(ptr(mid_o), ptr(mid_lse), self.base, ptr(k_cache), ptr(v_cache), k_cache.stride(0),
                                                k_cache.stride(1), v_cache.stride(0), v_cache.stride(1), ptr(req_to_token_indexs),
                                                req_to_token_indexs.stride(0), ptr(b_req_idx), ptr(b_seq_len), batch, Hq, Hkv, D,
-                                               max_len_in_batch, block_seq, dtype_tag(pool_layer), 0.0, self.base + self.off_flags,
-                                               sid, vb, s), "esp_decode_stage1_gated")
+                                               max_len_in_batch, block_seq, dtype_tag(pool_layer), 0.0, pool_layer.shape[0],
+                                               self.base + self.off_flags, sid, vb, s), "esp_decode_stage1_gated")
         mbase = self.peer_base[self.master]
         slot = self.rank
         _lib.check(lib.esp_decode_merge(mbase + self.off_o + slot * batch * Hq * D * 4, mbase + self.off_lse + slot * batch * Hq * 4,

@@ -63,7 +63,7 @@ def ring_context_attention(q, local_kv, o, m, l, *, rank: int, peers: Sequence[i
                            stride: int, max_len_in_batch: int, num_kv_heads: int, comm, recv_buffers,
                            attention_fn: Callable, init_fn: Callable, overlap: bool = True,
                            keep: Optional[KeepPlan] = None, pool_layer=None, layer_idx: int = 0,
-                           keep_fns=None):
+                           keep_fns=None, exchange=None):
     """One layer's ring pass on logical rank ``rank`` of the ring ``peers`` (SP ranks in ring order).
 
     q [Tq, Hq, D]; local_kv [max_token_num, 2*Hkv, D] (K heads then V heads); ``recv_buffers`` two
@@ -73,6 +73,10 @@ def ring_context_attention(q, local_kv, o, m, l, *, rank: int, peers: Sequence[i
     sends it on to rank+1 and receives the next one from rank-1 (:163,171).  With ``overlap`` the
     exchange of block i runs on the communicator's stream while block i is being attended to; without
     it the exchange is queued behind the kernel as in the reference's default mode (:464-465).
+
+    ``exchange`` (a ``peer_ring.CopyEngineRing``) replaces the NCCL pair by a copy-engine transfer into the next
+    instance's memory, synchronised by flags; the blocks then arrive in the exchange's own two buffers
+    (``recv_buffers`` and ``comm`` are not used), in the same order and with the same buffer swap.
     """
     P = len(peers)
     init_fn(o, m, l)
@@ -83,13 +87,21 @@ def ring_context_attention(q, local_kv, o, m, l, *, rank: int, peers: Sequence[i
     num_used = 0
     if keep is not None:
         keep.cur_kv_cache_index.zero_()
+    if exchange is not None and P > 1:
+        recv_buffers = exchange.receive_buffers(local_kv)
+        exchange.begin_pass(nxt_rank, prv_rank, P - 1)
+        kv_bytes = local_kv.numel() * local_kv.element_size()
+    else:
+        exchange = None
     for i in range(P):
         src = (rank - i) % P
         meta = metas[src]
         recv = None
         if i != P - 1:
             recv = recv_buffers[i % 2]
-            if overlap:
+            if exchange is not None:
+                exchange.forward(i, cur.data_ptr(), kv_bytes)      # overlaps the attention over the same block
+            elif overlap:
                 comm.wait_for_default_stream()      # block i is ready, the receive buffer is no longer read
                 comm.nccl_group_start()
                 comm.nccl_recv(recv, prv_rank)
@@ -98,7 +110,7 @@ def ring_context_attention(q, local_kv, o, m, l, *, rank: int, peers: Sequence[i
         attention_fn(q, cur[:, :Hkv, :], cur[:, Hkv:, :], o, metas[rank].start_loc, metas[rank].seq_len,
                      metas[rank].first_idx, meta.start_loc, meta.seq_len, meta.first_idx, stride,
                      max_len_in_batch, m, l)
-        if i != P - 1 and not overlap:
+        if i != P - 1 and not overlap and exchange is None:
             comm.wait_for_default_stream()
             comm.nccl_group_start()
             comm.nccl_recv(recv, prv_rank)
@@ -117,9 +129,17 @@ def ring_context_attention(q, local_kv, o, m, l, *, rank: int, peers: Sequence[i
             num_used += total
             if layer_idx == 0:
                 keep.cur_kv_cache_index += nl
-        if i != P - 1:
+        if exchange is not None:
+            if i > 0:
+                exchange.release(i - 1)             # the buffer that held this step's block may be refilled
+            if i != P - 1:
+                exchange.wait_arrival(i)            # the next block has arrived before it is read
+                cur = recv
+        elif i != P - 1:
             comm.let_default_stream_wait()          # the next block has arrived before it is read
             cur = recv
+    if exchange is not None:
+        exchange.end_pass()
     return o
 
 

@@ -1,7 +1,17 @@
-// Building-block check for the tcgen05.mma operand forms used by the prefill kernel:
-// one CTA computes D[128,128] = A[128,128] * B^T through an 8-step K=16 MMA chain.
-#include "esp_common.cuh"
-#include "sm100_ptx.cuh"
+// Test-only kernels, built into their own library by the test-suite (not part of the product library or its ABI).
+//
+// esp_selftest_umma: building-block check for the tcgen05.mma operand forms used by the prefill kernel: one CTA
+// computes D[128,128] fp32 = A[128,128] * B^T through an 8-step K=16 MMA chain.
+//   mode 0: A and B K-major in shared memory (the Q*K^T form);
+//   mode 1: A K-major, B MN-major in shared memory (B given as [K=128, N=128] row-major, the P*V form);
+//   mode 2: A converted to 16-bit and staged in tensor memory, B MN-major (the P*V form actually used).
+// esp_selftest_bounded_wait: the product's own bounded mbarrier wait (mbar_wait_bounded, the function every wait of
+// the prefill kernel goes through) on a barrier nothing ever completes: it must give up after `limit_cycles`, write 1
+// to *result_dev and return normally, leaving the context usable.  (2 would mean the barrier completed.)
+#include <type_traits>
+
+#include "../../loongserve_b200/csrc/esp_common.cuh"
+#include "../../loongserve_b200/csrc/sm100_ptx.cuh"
 
 namespace esp {
 using namespace ptx;
@@ -92,20 +102,16 @@ __global__ void __launch_bounds__(128, 1) selftest_umma_kernel(const T* __restri
     if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, 256); }
 }
 
-// One thread waits on an mbarrier that nobody ever arrives at, for at most `limit_cycles`, then records the
-// give-up in `result` (1 = timed out as intended, 2 = barrier unexpectedly completed) and returns normally.
-__global__ void selftest_bounded_wait_kernel(long long limit_cycles, int* result) {
+__device__ long long g_selftest_limit;
+
+__global__ void selftest_bounded_wait_kernel(int* result) {
     __shared__ __align__(8) unsigned long long s_bar;
     const uint32_t bar = smem_u32(&s_bar);
     if (threadIdx.x == 0) { mbar_init(bar, 1); fence_barrier_init(); }
     __syncthreads();
     if (threadIdx.x == 0) {
-        const long long t0 = clock64();
-        int r = 1;
-        while (clock64() - t0 < limit_cycles) {
-            if (mbar_try_wait(bar, 0)) { r = 2; break; }
-        }
-        *result = r;
+        const int r = mbar_wait_bounded(bar, 0, &g_selftest_limit, nullptr);
+        *result = r == 2 ? 1 : 2;
     }
 }
 
@@ -115,9 +121,10 @@ using namespace esp;
 
 extern "C" int esp_selftest_bounded_wait(int64_t limit_cycles, int32_t* result_dev, void* stream) {
     if (!result_dev || limit_cycles <= 0 || limit_cycles > 4000000000LL) return ESP_ERR_BAD_ARG;
-    selftest_bounded_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit_cycles, result_dev);
-    ESP_LAUNCH_CHECK("selftest_bounded_wait_kernel");
-    return ESP_OK;
+    const long long v = limit_cycles;
+    if (cudaMemcpyToSymbol(g_selftest_limit, &v, sizeof(v)) != cudaSuccess) return ESP_ERR_CUDA;
+    selftest_bounded_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(result_dev);
+    return cudaGetLastError() == cudaSuccess ? ESP_OK : ESP_ERR_CUDA;
 }
 
 extern "C" int esp_selftest_umma(const void* a, const void* b, float* d, int32_t mode, int32_t dtype, void* stream) {
@@ -125,14 +132,13 @@ extern "C" int esp_selftest_umma(const void* a, const void* b, float* d, int32_t
     const int smem = 65536 + 64 + 1024;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == ESP_DTYPE_F16) {
-        ESP_CUDA_TRY(cudaFuncSetAttribute(selftest_umma_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (cudaFuncSetAttribute(selftest_umma_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return ESP_ERR_CUDA;
         selftest_umma_kernel<__half><<<1, 128, smem, s>>>((const __half*)a, (const __half*)b, d, mode);
     } else if (dtype == ESP_DTYPE_BF16) {
-        ESP_CUDA_TRY(cudaFuncSetAttribute(selftest_umma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (cudaFuncSetAttribute(selftest_umma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return ESP_ERR_CUDA;
         selftest_umma_kernel<__nv_bfloat16><<<1, 128, smem, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, d, mode);
     } else {
         return ESP_ERR_BAD_ARG;
     }
-    ESP_LAUNCH_CHECK("selftest_umma_kernel");
-    return ESP_OK;
+    return cudaGetLastError() == cudaSuccess ? ESP_OK : ESP_ERR_CUDA;
 }

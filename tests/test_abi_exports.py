@@ -57,9 +57,9 @@ def test_error_strings_and_argument_checks(built):
     assert lib.esp_strerror(0) == b"ok"
     assert b"unsupported" in lib.esp_strerror(-5)
     # argument validation happens on the host before any CUDA call
-    assert lib.esp_kv_scatter(None, 0, 0, None, 0, 0, None, 0, 5, 1, 8, 2, None) == -1
+    assert lib.esp_kv_scatter(None, 0, 0, None, 0, 0, None, 0, 5, 1, 8, 2, 0, None) == -1
     assert lib.esp_decode_merge(None, None, None, None, None, 1, 1, 128, 1, 1, 2, None) == -1
-    assert lib.esp_kv_scatter(None, 0, 0, None, 0, 0, None, 0, 0, 1, 8, 2, None) == 0     # empty input is a no-op
+    assert lib.esp_kv_scatter(None, 0, 0, None, 0, 0, None, 0, 0, 1, 8, 2, 0, None) == 0     # empty input is a no-op
 
 
 def test_ops_refuse_cpu_tensors(built):

@@ -8,16 +8,15 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("mode", [0, 1, 2])
-def test_umma_forms(mode, dtype):
-    from loongserve_b200 import _lib
+def test_umma_forms(mode, dtype, selftest_lib):
     from loongserve_b200._util import dtype_tag
     g = torch.Generator().manual_seed(mode)
     a = torch.randn(128, 128, generator=g).to(dtype).cuda()
     b = torch.randn(128, 128, generator=g).to(dtype).cuda()
     d = torch.zeros(128, 128, device="cuda")
-    rc = _lib.attn().esp_selftest_umma(a.data_ptr(), b.data_ptr(), d.data_ptr(), mode, dtype_tag(a),
-                                       torch.cuda.current_stream().cuda_stream)
-    _lib.check(rc, "esp_selftest_umma")
+    rc = selftest_lib.esp_selftest_umma(a.data_ptr(), b.data_ptr(), d.data_ptr(), mode, dtype_tag(a),
+                                        torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
     torch.cuda.synchronize()
     ref = a.float() @ (b.float().t() if mode == 0 else b.float())
     assert not bool(torch.isnan(d).any()), "MMA chain timed out"
