@@ -11,11 +11,13 @@ value = algorithmic TFLOP/s of the whole job: 4*D*H*T*(T+1)/2 FLOP per step / de
 
 The same JSON line carries: `roofline` (tensor-core bound, against the measured cuBLAS bf16 peak),
 `e2e` (same metric through the public Python API with HOST pinned inputs copied in and the output
-copied back inside the timed region), `cpu_baseline` (the CPU oracle on a bounded sample, rank 0,
-N=1 only), `decode` (distributed flash-decoding, HBM-bound, N=1 only: batch 64, lengths U[4096,65536],
-token-indexed pool with shuffled slots) and `clocks`.
+copied back inside the timed region), `cpu_baseline` (PyTorch scaled_dot_product_attention on the host cores over a
+bounded sample, checked against the CPU oracle; rank 0, N=1 only), `decode` (distributed flash-decoding, HBM-bound:
+batch 64, lengths U[4096,65536], token-indexed pools with shuffled slots, KV split over the N instances), `clocks`,
+and -- at N > 1 -- `parity_check`: sampled rows of the ring result, of the host-buffer result and of both decode
+exchanges recomputed in fp32 from K/V gathered over all ranks; a miss makes the run exit non-zero.
 
-`--impl reference` times the CPU restatement of the reference path (oracle/) on the host cores.
+`--impl reference` times the reference path's CPU form (PyTorch SDPA, checked against oracle/) on the host cores.
 """
 from __future__ import annotations
 
@@ -134,48 +136,164 @@ def use_all_host_cores(torch) -> int:
     return torch.get_num_threads()
 
 
-def run_reference_arm(args):
-    """The reference path's CPU implementation (the oracle restatement) on the host cores."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    import torch
+def cpu_sdpa_sample(torch, Ts: int, repeats: int, warmup: int):
+    """Causal attention of one `Ts`-token sequence at the benchmark's layer shape on the host cores with
+    torch.nn.functional.scaled_dot_product_attention(is_causal=True), all heads in one call (bf16 inputs as in the GPU
+    arm).  The result is checked against the CPU oracle's ring step on sampled heads.  Returns (seconds per call, check)."""
+    import torch.nn.functional as F
     from oracle import esp_oracle as O
-    cores = use_all_host_cores(torch)
-    Ts = int(os.environ.get("ESP_BENCH_CPU_TOKENS", "8192"))
     g = torch.Generator().manual_seed(0)
     q = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
     k = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
     v = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
-    ln = torch.tensor([Ts], dtype=torch.int32); z = torch.zeros(1, dtype=torch.int32)
+    qh, kh, vh = (x.transpose(0, 1).unsqueeze(0).contiguous() for x in (q, k, v))      # [1, H, Ts, D]
 
     def step():
-        o = torch.zeros(Ts, H, D, dtype=torch.bfloat16)
-        m = torch.full((Ts, H), float("-inf")); l = torch.zeros(Ts, H)
-        O.ring_step(q, k, v, o, m, l, z, ln, z, z, ln, z, 1)
-        return o
+        return F.scaled_dot_product_attention(qh, kh, vh, is_causal=True)
 
-    for _ in range(args.warmup):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step()
-    dt = (time.perf_counter() - t0) / args.steps
+    for _ in range(warmup):
+        out = step()
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        out = step()
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    # the oracle checks the timed implementation on two heads and the first rows of the same sample (a causal row only
+    # sees the keys before it, so the first Tc rows are a complete problem of their own)
+    hs = [0, H - 1]
+    Tc = min(Ts, 8192)
+    ln = torch.tensor([Tc], dtype=torch.int32); z = torch.zeros(1, dtype=torch.int32)
+    o = torch.zeros(Tc, len(hs), D); m = torch.full((Tc, len(hs)), float("-inf")); l = torch.zeros(Tc, len(hs))
+    O.ring_step(q[:Tc, hs].float(), k[:Tc, hs].float(), v[:Tc, hs].float(), o, m, l, z, ln, z, z, ln, z, 1)
+    got = out[0, hs, :Tc].transpose(0, 1).float()
+    err = float((got - o).abs().max())
+    return best, {"max_abs_err_vs_oracle": err, "ok": bool(err <= 2e-2 + 1e-2 * float(o.abs().max()))}
+
+
+def cpu_tokens_default() -> int:
+    return int(os.environ.get("ESP_BENCH_CPU_TOKENS", "65536"))
+
+
+def run_reference_arm(args):
+    """The reference path on the host cores: PyTorch scaled_dot_product_attention(is_causal=True), the CPU form of the
+    same causal attention the reference itself checks its kernel against (torch_att,
+    ring_context_flashattention_nopad.py:287-321), over a bounded sample of the workload, FLOP-normalised."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    cores = use_all_host_cores(torch)
+    Ts = cpu_tokens_default()
+    t_all0 = time.perf_counter()
+    dt, chk = cpu_sdpa_sample(torch, Ts, repeats=max(1, args.steps), warmup=max(1, min(args.warmup, 2)))
     val = prefill_flops(Ts) / dt / 1e12
-    sample = f"one causal ring step over {Ts} tokens x {H} heads x {D} (bf16 inputs, fp32 math), FLOP-normalised"
+    sample = (f"torch.nn.functional.scaled_dot_product_attention(is_causal=True), one sequence of {Ts} tokens x {H} heads x {D} "
+              f"(bf16), best of {max(1, args.steps)} calls, FLOP-normalised; checked against the CPU oracle on 2 heads x 8192 rows")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"ring causal prefill attention, 1 seq x {T_TOTAL} tokens, {H}x{D}, striped over N GPUs",
-                   "note": "CPU arm runs a bounded sample of the same step"},
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+                   "note": "CPU arm runs a bounded sample of the same step",
+                   "cpu_tokens": Ts, "cpu_tokens_source": "ESP_BENCH_CPU_TOKENS" if "ESP_BENCH_CPU_TOKENS" in os.environ else "default"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "reference", "sample": sample, "check": chk},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "wall_s": time.perf_counter() - t_all0,
     }), flush=True)
 
 
 # ------------------------------------------------------------------------------------------------
+# Parity of what the timed regions computed, against fp32 attention over K/V gathered from all ranks.
+# Tolerances: attention output 2e-2 abs + 1e-2 rel (bf16), lse 1e-3 abs + 1e-3 rel.
+def _tol_o(got, ref):
+    return bool(((got - ref).abs() <= 2e-2 + 1e-2 * ref.abs()).all())
+
+
+def _tol_lse(got, ref):
+    return abs(got - ref) <= 1e-3 + 1e-3 * abs(ref)
+
+
+def ring_parity(torch, dist, P, q, kv_local, o, lse, local_len, first, stride, striped, heads=(0, H - 1), n_rows=12):
+    """Sampled local rows of this rank's ring result, recomputed in fp32 on the device from the K/V rows of all ranks
+    (one head at a time, gathered with all_gather).  Returns (summary, references) -- the references are reused to check
+    the host-buffer run of the same inputs."""
+    Tl = q.shape[0]
+    max_tok = kv_local.shape[0]
+    T = sum(x[0] for x in local_len)
+    rows = sorted(set([0, 1, Tl - 1, Tl - 2] + [int(i * (Tl - 1) / (n_rows - 1)) for i in range(n_rows)]))
+    rows = [r for r in rows if 0 <= r < Tl]
+    scale = D ** -0.5
+    worst_o = worst_l = 0.0
+    ok = True
+    refs = []
+    for h in heads:
+        parts = []
+        for c in (h, H + h):
+            mine = kv_local[:, c].contiguous()
+            if P > 1:
+                allr = torch.empty((P * max_tok, D), dtype=mine.dtype, device=mine.device)
+                dist.all_gather_into_tensor(allr, mine)
+            else:
+                allr = mine
+            allr = allr.view(P, max_tok, D)
+            if striped:
+                glob = allr.transpose(0, 1).reshape(P * max_tok, D)[:T]          # token t = row t // P of rank t % P
+            else:
+                glob = torch.cat([allr[r, :local_len[r][0]] for r in range(P)], 0)
+            parts.append(glob)
+        Kg, Vg = parts
+        for r in rows:
+            gidx = first + r * stride                   # global position of local row r
+            sc = (Kg[:gidx + 1].float() @ q[r, h].float()) * scale
+            ref_lse = float(torch.logsumexp(sc, 0))
+            ref_o = torch.softmax(sc, 0) @ Vg[:gidx + 1].float()
+            got = o[r, h].float()
+            worst_o = max(worst_o, float((got - ref_o).abs().max()))
+            worst_l = max(worst_l, abs(float(lse[r, h]) - ref_lse))
+            ok = ok and _tol_o(got, ref_o) and _tol_lse(float(lse[r, h]), ref_lse)
+            refs.append((r, h, ref_o.cpu()))
+        del Kg, Vg, parts
+    return {"ok": ok, "max_abs_err": worst_o, "max_lse_err": worst_l, "rows": len(rows) * len(heads)}, refs
+
+
+def decode_parity(torch, dist, rank, P, q, pool, rt, loc_all, out, out_lse, reqs, heads=(0, H - 1)):
+    """Merged (o, lse) of sampled requests and heads on the master against one fp32 softmax over the request's K/V rows
+    gathered from every instance.  Every rank takes part in the gathers; rank 0 returns the summary."""
+    scale = D ** -0.5
+    worst_o = worst_l = 0.0
+    ok = True
+    n = 0
+    for b in reqs:
+        mx = max(loc_all[r][b] for r in range(P))
+        for h in heads:
+            kv_parts = []
+            for c in (h, H + h):
+                mine = torch.zeros((mx, D), dtype=pool.dtype, device=pool.device)
+                nloc = loc_all[rank][b]
+                mine[:nloc] = pool[rt[b, :nloc].long(), c]
+                allr = torch.empty((P * mx, D), dtype=pool.dtype, device=pool.device)
+                dist.all_gather_into_tensor(allr, mine)
+                allr = allr.view(P, mx, D)
+                kv_parts.append(torch.cat([allr[r, :loc_all[r][b]] for r in range(P)], 0))
+            if rank == 0:
+                Kb, Vb = kv_parts
+                sc = (Kb.float() @ q[b, h].float()) * scale
+                ref_lse = float(torch.logsumexp(sc, 0))
+                ref_o = torch.softmax(sc, 0) @ Vb.float()
+                got = out[b, h].float()
+                worst_o = max(worst_o, float((got - ref_o).abs().max()))
+                worst_l = max(worst_l, abs(float(out_lse[b, h]) - ref_lse))
+                ok = ok and _tol_o(got, ref_o) and _tol_lse(float(out_lse[b, h]), ref_lse)
+                n += 1
+    return {"ok": ok, "max_abs_err": worst_o, "max_lse_err": worst_l, "rows": n}
+
+
+# ------------------------------------------------------------------------------------------------
+def decode_block_default() -> int:
+    return int(os.environ.get("ESP_BENCH_DECODE_BLOCK", "2048"))
+
+
 def decode_bench(torch, peaks, steps=10, warmup=3, B=64):
     """Distributed flash-decoding on one instance: stage 1 + merge over a shuffled token-indexed pool."""
     from loongserve_b200 import flash_decoding as fd
@@ -199,7 +317,7 @@ def decode_bench(torch, peaks, steps=10, warmup=3, B=64):
     rt = rt.to(dev)
     b_req = torch.arange(B, dtype=torch.int32, device=dev); b_len = lens.to(torch.int32).to(dev)
     k, v = pool[:, :H], pool[:, H:]
-    bs = int(os.environ.get("ESP_BENCH_DECODE_BLOCK", "2048"))
+    bs = decode_block_default()
     nblk = (mx + bs - 1) // bs
     mid_o = torch.empty(nblk, B, H, D, device=dev); mid_l = torch.empty(nblk, B, H, device=dev)
     o = torch.empty(B, H, D, dtype=torch.bfloat16, device=dev); lse = torch.empty(B, H, device=dev)
@@ -233,7 +351,7 @@ def decode_bench(torch, peaks, steps=10, warmup=3, B=64):
 
 
 def decode_bench_dist(torch, dist, comm, peaks, rank, P, steps=10, warmup=3, B=64, fused=False):
-    """Distributed flash-decoding over P instances (BASELINE config 3): every request's tokens are split
+    """Distributed flash-decoding over P instances: every request's tokens are split
     evenly over the instances (token t on instance t mod P), instance 0 is the master.  A step is the
     whole exchange: q broadcast -> split-KV stage 1 on every instance -> peers merge and send fp32
     (o, lse) -> master merges.  Returned GB/s = all instances' algorithmic bytes / max-over-ranks time."""
@@ -259,7 +377,7 @@ def decode_bench_dist(torch, dist, comm, peaks, rank, P, steps=10, warmup=3, B=6
     rt = rt.to(dev)
     b_req = torch.arange(B, dtype=torch.int32, device=dev)
     b_len = torch.tensor(loc, dtype=torch.int32, device=dev)
-    bs = int(os.environ.get("ESP_BENCH_DECODE_BLOCK", "2048"))
+    bs = decode_block_default()
     nblk = (mx + bs - 1) // bs
     f32 = dict(dtype=torch.float32, device=dev)
     master = peer = None
@@ -314,14 +432,19 @@ def decode_bench_dist(torch, dist, comm, peaks, rank, P, steps=10, warmup=3, B=6
     nparts = sum(int(((max(0, (int(L) - r + P - 1) // P)) + bs - 1) // bs) for L in lens for r in range(P))
     alg_bytes = float(total) * (2 * H * D * 2) + float(total) * 4 + P * B * H * D * 2 + nparts * H * (D + 1) * 4
     gbs = alg_bytes / (ms * 1e-3) / 1e9
-    status = None
+    # what the last step produced, against fp32 over the K/V rows of all instances
+    loc_all = [[(int(L) - r + P - 1) // P for L in lens] for r in range(P)]
+    lse_t = f_lse if fused else (master.global_out_lse if rank == 0 else None)
+    parity = decode_parity(torch, dist, rank, P, q, pool, rt, loc_all, out, lse_t, reqs=(0, B // 2, B - 1))
+    from loongserve_b200 import flash_decoding as fd_
+    status = list(fd_.device_status(clear=True))
     if grp is not None:
-        status = list(grp.device_status())
         dist.barrier()
         grp.close()
     del pool
     torch.cuda.empty_cache()
     return {"metric": "distributed_decode_attention_hbm_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "n_gpus": P,
+            "parity": parity,
             "exchange": "peer memory (NVLink stores + flags in the kernels)" if fused else "NCCL send/recv", "device_status": status,
             "config": {"workload": f"batch {B} x U[4096,65536] tokens ({total} total) split evenly over {P} instances, 1 master, "
                                    f"{H}x{D} bf16, shuffled token-indexed pools, split {bs}; step = q broadcast + stage 1 + (o,lse) gather + merge"},
@@ -363,21 +486,24 @@ def scatter_bench(torch, peaks, steps=10, warmup=3, tokens=262144):
             "algorithmic_bytes": alg}
 
 
-def e2e_llama(args):
-    """End-to-end Llama-2-7B-architecture run (the fifth benchmark configuration when launched on 8 GPUs): one
+def e2e_llama(args, dist=None, comm=None, graph=None):
+    """End-to-end Llama-2-7B-architecture run: one
     prefill of `--e2e-tokens` uniform-random token ids striped over the N instances, then `--e2e-decode-steps`
     decode steps with the KV distributed over all instances (instance 0 is the master and keeps the new tokens).
     Random-init bf16 weights, seeded; projections are cuBLAS, everything else this package's kernels."""
     import torch
-    import torch.distributed as dist
     from loongserve_b200.attention_runtime import ESPAttentionRuntime
     from loongserve_b200.llama_stack import LlamaConfig, LlamaESPStack, LlamaWeights
     world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    comm = None
-    if world > 1:
+    own_group = dist is None            # called on its own: set up (and later tear down) the process group here
+    use_graph = bool(args.e2e_graph) if graph is None else bool(graph)
+    exchange_kind = "peer_memory" if use_graph else args.e2e_exchange
+    if own_group:
+        import torch.distributed as dist
+    if world > 1 and own_group:
         dist.init_process_group("nccl", device_id=dev)
         from loongserve_b200 import rnccl
         idt = torch.zeros(128, dtype=torch.uint8, device=dev)
@@ -394,12 +520,8 @@ def e2e_llama(args):
                              max_seq_length=max_tok + steps + 64, sp_world_size=P, total_rank=rank, sp_comm=comm,
                              dtype=torch.bfloat16, device=dev, decode_block_seq=1024)
     stack = LlamaESPStack(cfg, LlamaWeights(cfg, torch.bfloat16, dev, seed=0), rt)
-    if args.e2e_exchange == "peer_memory" and world > 1:
-        def gather(b):
-            lst = [None] * world
-            dist.all_gather_object(lst, b)
-            return lst
-        rt.enable_peer_memory_decode(0, gather, max_batch=1)
+    if exchange_kind == "peer_memory" and world > 1:
+        rt.enable_peer_memory_decode(0, _gather_fn(dist, world), max_batch=1)
     g = torch.Generator(device=dev).manual_seed(7)
     ids_all = torch.randint(0, cfg.vocab, (T,), generator=g, device=dev)        # same stream on every rank
     ids = ids_all[rank::P].contiguous()
@@ -438,7 +560,7 @@ def e2e_llama(args):
     local_cnt = Tl
     tok = i32([1])
     graphed = None
-    if args.e2e_graph and world > 1 and steps > 0:
+    if use_graph and world > 1 and steps > 0:
         from loongserve_b200.llama_stack import GraphedDecode
         graphed = GraphedDecode(stack, rt._fused_groups[0], b_req, i32([local_cnt]), positions=i32([T]) if rank == 0 else None,
                                 max_new_tokens=steps).capture()
@@ -466,27 +588,34 @@ def e2e_llama(args):
     if world > 1:
         dist.barrier()
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    res = None
     if rank == 0:
         pre_ms, dec_ms, bad = (float(x) for x in t.tolist())
         attn_flops = cfg.num_layers * 4.0 * cfg.head_dim * cfg.num_q_heads * T * (T + 1) / 2.0
-        print(json.dumps({
+        res = {
             "metric": "e2e_llama_prefill_tokens_per_s", "value": T / (pre_ms * 1e-3), "unit": "tokens/s", "n_gpus": P,
             "prefill_ms": pre_ms, "decode_ms_per_step": dec_ms, "decode_steps": steps, "higher_is_better": True,
-            "dtype": "bf16", "data": "synthetic", "outputs_finite": bad == 0.0, "decode_exchange": args.e2e_exchange, "decode_graph": bool(args.e2e_graph),
+            "dtype": "bf16", "data": "synthetic", "outputs_finite": bad == 0.0, "decode_exchange": exchange_kind, "decode_graph": use_graph,
             "last_logits_checksum": float(last_logit_sum),
             "prefill_attention_tflops_equiv": attn_flops / (pre_ms * 1e-3) / 1e12,
             "config": {"workload": f"Llama-2-7B architecture ({cfg.num_layers} layers, hidden {cfg.hidden}, {cfg.num_q_heads} heads x {cfg.head_dim}, "
                                    f"FFN {cfg.ffn}, vocab {cfg.vocab}), random-init bf16 weights; one {T}-token prefill at ESP={P} (striped), "
-                                   f"then {steps} decode steps with the KV distributed over all {P} GPUs"}}), flush=True)
+                                   f"then {steps} decode steps with the KV distributed over all {P} GPUs"}}
+        if own_group:
+            print(json.dumps(res), flush=True)
     if world > 1:
         dist.barrier()
         rt.close()
-        comm.close()
-        dist.destroy_process_group()
+        if own_group:
+            comm.close()
+            dist.destroy_process_group()
+    del stack, rt
+    torch.cuda.empty_cache()
+    return res
 
 
 def varlen_bench(args):
-    """Packed varlen prefill plus token-granular KV scatter on one GPU (fourth benchmark configuration at P=1):
+    """Packed varlen prefill plus token-granular KV scatter on one GPU:
     16 sequences with lengths log-uniform in [1024, 262144] (seeded), bf16, 32 heads x 128, causal; then every
     token's K/V row is scattered into shuffled pool slots.  Sampled rows are recomputed in fp32 on the device."""
     import torch
@@ -543,13 +672,16 @@ def varlen_bench(args):
     torch.cuda.synchronize()
     sms = e0.elapsed_time(e1) / args.steps
     exact = bool(torch.equal(pool[dest[::997].long()], kv[::997]))
-    print(json.dumps({"metric": "varlen_prefill_attention_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-                      "dtype": "bf16", "data": "synthetic", "max_abs_err_sampled_rows": worst,
-                      "scatter": {"value": T * (2 * 2 * H * D * 2 + 4) / (sms * 1e-3) / 1e9, "unit": "GB/s", "ms": sms, "bit_exact_sample": exact},
-                      "config": {"workload": f"16 packed sequences, lengths log-uniform in [1024, 262144] (seed 0): {lens}; {T} tokens, "
-                                             f"{H}x{D} bf16 causal, then all K/V rows scattered to shuffled int32 slots"},
-                      "device_status": list(ca.device_status())}), flush=True)
+    res = {"metric": "varlen_prefill_attention_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+           "dtype": "bf16", "data": "synthetic", "max_abs_err_sampled_rows": worst,
+           "scatter": {"value": T * (2 * 2 * H * D * 2 + 4) / (sms * 1e-3) / 1e9, "unit": "GB/s", "ms": sms, "bit_exact_sample": exact},
+           "config": {"workload": f"16 packed sequences, lengths log-uniform in [1024, 262144] (seed 0): {lens}; {T} tokens, "
+                                  f"{H}x{D} bf16 causal, then all K/V rows scattered to shuffled int32 slots"},
+           "device_status": list(ca.device_status())}
+    del q, kv, o, m, l, pool
+    torch.cuda.empty_cache()
+    return res
 
 
 def ops_bench(args):
@@ -595,25 +727,21 @@ def ops_bench(args):
 
 
 def cpu_baseline(torch):
-    from oracle import esp_oracle as O
-    use_all_host_cores(torch)
-    Ts = int(os.environ.get("ESP_BENCH_CPU_TOKENS", "8192"))
-    g = torch.Generator().manual_seed(0)
-    q = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
-    k = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
-    v = torch.randn(Ts, H, D, generator=g).to(torch.bfloat16)
-    ln = torch.tensor([Ts], dtype=torch.int32); z = torch.zeros(1, dtype=torch.int32)
-    best = None
-    for it in range(3):
-        o = torch.zeros(Ts, H, D, dtype=torch.bfloat16)
-        m = torch.full((Ts, H), float("-inf")); l = torch.zeros(Ts, H)
-        t0 = time.perf_counter()
-        O.ring_step(q, k, v, o, m, l, z, ln, z, z, ln, z, 1)
-        dt = time.perf_counter() - t0
-        if it > 0:
-            best = dt if best is None else min(best, dt)
-    return {"value": prefill_flops(Ts) / best / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"one causal ring step over {Ts} tokens x {H} heads x {D} (bf16 inputs, fp32 math, torch CPU), best of 2 after 1 warm-up, FLOP-normalised"}
+    cores = use_all_host_cores(torch)
+    Ts = cpu_tokens_default()
+    dt, chk = cpu_sdpa_sample(torch, Ts, repeats=2, warmup=1)
+    return {"value": prefill_flops(Ts) / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "reference",
+            "sample": f"torch.nn.functional.scaled_dot_product_attention(is_causal=True) on the host cores, one sequence of {Ts} tokens x "
+                      f"{H} heads x {D} (bf16), best of 2 after 1 warm-up, FLOP-normalised; checked against the CPU oracle on 2 heads x 8192 rows",
+            "check": chk, "cpu_tokens_source": "ESP_BENCH_CPU_TOKENS" if "ESP_BENCH_CPU_TOKENS" in os.environ else "default"}
+
+
+def _gather_fn(dist, world):
+    def gather(b):
+        lst = [None] * world
+        dist.all_gather_object(lst, b)
+        return lst
+    return gather
 
 
 def main():
@@ -624,7 +752,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=T_TOTAL)
     ap.add_argument("--layout", default="striped", choices=["striped", "contiguous"])
-    ap.add_argument("--no-overlap", action="store_true")
+    ap.add_argument("--exchange", default="copy_engine", choices=["copy_engine", "nccl"],
+                    help="ring exchange at N > 1: copy-engine transfers into peer memory, or ncclSend/ncclRecv")
+    ap.add_argument("--no-overlap", action="store_true", help="NCCL exchange only: queue it behind the attention kernel")
     ap.add_argument("--skip-extras", action="store_true", help="skip e2e / decode / cpu baseline (profiling runs)")
     ap.add_argument("--decode-only", action="store_true", help="run only the decode part (profiling runs)")
     ap.add_argument("--decode-batch", type=int, default=64)
@@ -634,12 +764,12 @@ def main():
     ap.add_argument("--e2e-tokens", type=int, default=524288)
     ap.add_argument("--e2e-decode-steps", type=int, default=128)
     ap.add_argument("--e2e-layers", type=int, default=32)
-    ap.add_argument("--e2e-head-chunks", type=int, default=0,
-                    help="head chunks of the pipelined host-buffer leg (default 8 on one GPU, else 4)")
+    ap.add_argument("--e2e-head-chunks", type=int, default=8, help="head chunks of the pipelined host-buffer leg")
     ap.add_argument("--e2e-graph", action="store_true",
                     help="end-to-end run: replay the decode step as one CUDA graph per instance (implies --e2e-exchange peer_memory)")
     ap.add_argument("--e2e-exchange", default="nccl", choices=["nccl", "peer_memory"],
                     help="decode exchange of the end-to-end run: NCCL messages or NVLink stores + flags in the kernels")
+    ap.add_argument("--no-llama", action="store_true", help="8-GPU run: leave out the end-to-end Llama-architecture extra")
     args = ap.parse_args()
     if args.e2e:
         if args.e2e_graph:
@@ -647,7 +777,7 @@ def main():
         e2e_llama(args)
         return
     if args.varlen:
-        varlen_bench(args)
+        print(json.dumps(varlen_bench(args)), flush=True)
         return
     if args.ops_only:
         ops_bench(args)
@@ -664,6 +794,7 @@ def main():
     import torch
     import torch.distributed as dist
     from loongserve_b200 import context_attention as ca
+    from loongserve_b200 import flash_decoding as fd
     from loongserve_b200 import ring as ringmod
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -692,7 +823,11 @@ def main():
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     q = torch.randn(Tl, H, D, generator=g, device=dev, dtype=torch.bfloat16)
     kv_local = torch.randn(max_tok, 2 * H, D, generator=g, device=dev, dtype=torch.bfloat16)
-    recv = [torch.empty_like(kv_local) for _ in range(2 if P > 1 else 0)]
+    exchange = None
+    if P > 1 and args.exchange == "copy_engine":
+        from loongserve_b200.peer_ring import CopyEngineRing
+        exchange = CopyEngineRing(rank, P, kv_local.numel() * 2, _gather_fn(dist, world), device=dev)
+    recv = [torch.empty_like(kv_local) for _ in range(2 if (P > 1 and exchange is None) else 0)]
     o = torch.empty_like(q)
     m = torch.empty(Tl, H, device=dev); l = torch.empty(Tl, H, device=dev)
 
@@ -709,7 +844,7 @@ def main():
             ringmod.ring_context_attention(q, kv_local, o, m, l, rank=rank, peers=list(range(P)), metas=metas,
                                            stride=stride, max_len_in_batch=Tl, num_kv_heads=H, comm=comm,
                                            recv_buffers=recv, attention_fn=ca.context_attention_fwd, init_fn=init_fn,
-                                           overlap=not args.no_overlap)
+                                           overlap=not args.no_overlap, exchange=exchange)
 
     sampler = ClockSampler(local_rank)
     sampler.start()                      # nvidia-smi needs a second to start: launch it before the warm-up
@@ -735,9 +870,16 @@ def main():
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
         ms = float(tms.item())
     st = ca.device_status()
+    st_flags = fd.device_status(clear=True)
     flops = prefill_flops(T)
     value = flops / (ms * 1e-3) / 1e12
     per_gpu = value / P
+
+    # ---- what the timed steps left in (o, m, l), against fp32 over the K/V rows of all ranks
+    parity = {}
+    lse = ca.attention_lse(m, l)
+    parity["ring"], refs = ring_parity(torch, dist, P, q, kv_local, o, lse, local_len, first[rank][0], stride, striped)
+    del lse
 
     # ---- end to end through the public API with host buffers (every step: H2D inputs, D2H output)
     e2e = None
@@ -748,14 +890,15 @@ def main():
 
         # the public host-buffer call: chunks of heads pipelined over the copy engines and the ring
         from loongserve_b200.host_pipeline import HostPrefillPipeline
-        chunks = args.e2e_head_chunks or (8 if P == 1 else 4)
+        chunks = args.e2e_head_chunks
         o_sample = o[:512].clone()                   # rows of the device-resident run, to check the host-buffer result against
         del o, m, l
         recv.clear()
         del q, kv_local
         torch.cuda.empty_cache()
         pipe = HostPrefillPipeline(Tl, max_tok, H, H, D, rank=rank, peers=list(range(P)), metas=metas, stride=stride,
-                                   max_len_in_batch=Tl, comm=comm, head_chunks=chunks, device=dev, overlap=not args.no_overlap)
+                                   max_len_in_batch=Tl, comm=comm, head_chunks=chunks, device=dev, overlap=not args.no_overlap,
+                                   exchange=exchange)
 
         def e2e_step():
             pipe.run(hq, hkv, ho)
@@ -774,6 +917,13 @@ def main():
             tms = torch.tensor([ems], device=dev)
             dist.all_reduce(tms, op=dist.ReduceOp.MAX)
             ems = float(tms.item())
+        worst = 0.0
+        ok = True
+        for r, h, ref_o in refs:
+            got = ho[r, h].float()
+            worst = max(worst, float((got - ref_o).abs().max()))
+            ok = ok and _tol_o(got, ref_o)
+        parity["e2e"] = {"ok": ok, "max_abs_err": worst, "rows": len(refs)}
         e2e = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": (hq.numel() + hkv.numel()) * 2 * P, "d2h_bytes_per_step": ho.numel() * 2 * P,
                "ms_per_step": ems, "steps": n_e2e, "head_chunks": chunks,
@@ -781,22 +931,50 @@ def main():
                "api": "loongserve_b200.host_pipeline.HostPrefillPipeline.run(pinned q, kv, o)"}
         del hq, hkv, ho, pipe
         torch.cuda.empty_cache()
+    st_flags2 = fd.device_status(clear=True)
+    if exchange is not None:
+        dist.barrier()
+        exchange.close()
 
-    decode_dist = decode_fused = None
+    decode_nccl = decode_peer = None
     if not args.skip_extras and P > 1:
         torch.cuda.empty_cache()
-        decode_dist = decode_bench_dist(torch, dist, comm, peaks, rank, P)
-        decode_fused = decode_bench_dist(torch, dist, comm, peaks, rank, P, fused=True)
+        decode_nccl = decode_bench_dist(torch, dist, comm, peaks, rank, P)
+        decode_peer = decode_bench_dist(torch, dist, comm, peaks, rank, P, fused=True)
+        if rank == 0:
+            parity["decode"] = decode_peer.pop("parity")
+            parity["decode_nccl"] = decode_nccl.pop("parity")
+
+    # every rank's verdict counts: a miss anywhere fails the run
+    all_ok = all(v.get("ok", False) for v in parity.values()) and st[0] == 0 and st_flags[0] == 0 and st_flags2[0] == 0
+    if world > 1:
+        okt = torch.tensor([1 if all_ok else 0], device=dev)
+        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+        worst_t = torch.tensor([parity["ring"]["max_abs_err"], parity["ring"]["max_lse_err"],
+                                parity.get("e2e", {}).get("max_abs_err", 0.0)], device=dev)
+        dist.all_reduce(worst_t, op=dist.ReduceOp.MAX)
+        all_ok = bool(okt.item())
+        parity["ring"]["max_abs_err"], parity["ring"]["max_lse_err"] = float(worst_t[0]), float(worst_t[1])
+        parity["ring"]["rows"] *= P
+        if "e2e" in parity:
+            parity["e2e"]["max_abs_err"] = float(worst_t[2]); parity["e2e"]["rows"] *= P
+    parity["all_ranks_ok"] = all_ok
+    parity["tolerance"] = "o: 2e-2 abs + 1e-2 rel; lse: 1e-3 abs + 1e-3 rel; against fp32 attention over the K/V rows of all ranks"
 
     if rank == 0:
+        exch = "single GPU" if P == 1 else ("copy-engine transfers into peer memory, flag-synchronised" if exchange is not None else
+                                            f"{'overlapped' if not args.no_overlap else 'serialised'} NCCL send/recv")
         out = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": P, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": f"ring causal prefill attention, 1 seq x {T} tokens, {H} q/kv heads x {D}, bf16, "
-                                   f"{args.layout} over {P} GPU(s), {'overlapped' if not args.no_overlap else 'serialised'} NCCL ring",
+                                   f"{args.layout} over {P} GPU(s)",
+                       "ring_exchange": exch,
                        "l2": "inputs (q 2 GiB + kv 4 GiB per job) far larger than L2, no flush needed",
-                       "flop_per_step": flops},
+                       "flop_per_step": flops,
+                       "env_overrides": {k: os.environ[k] for k in ("ESP_BENCH_CPU_TOKENS", "ESP_BENCH_DECODE_BLOCK", "ESP_ATTENTION_LIB")
+                                         if k in os.environ}},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tf_sustained"], "unit": "TFLOP/s",
                          "frac": per_gpu / peaks["tf_sustained"],
                          "traffic": PREFILL_TRAFFIC_262144_1GPU if (P == 1 and T == T_TOTAL) else None,
@@ -804,24 +982,38 @@ def main():
                          "peak_kind": "sustained cuBLAS bf16 (kernel runs for seconds inside the timed loop)",
                          "frac_of_burst_peak": per_gpu / peaks["tf_burst"], "per_gpu": True},
             "clocks": clocks,
-            "gpu_launches": args.steps * (1 + P),
-            "device_status": list(st),
+            "gpu_launches": args.steps * (1 + P) + (args.steps * 4 * (P - 1) if exchange is not None else 0),
+            "device_status": list(st), "flag_wait_status": [list(st_flags), list(st_flags2)],
+            "parity_check": parity,
         }
         if e2e is not None:
             out["e2e"] = e2e
-        if decode_dist is not None:
-            out["decode"] = decode_dist
-            out["decode_peer_memory"] = decode_fused
+        if decode_peer is not None:
+            out["decode"] = decode_peer
+            out["decode_nccl"] = decode_nccl
         if not args.skip_extras and P == 1:
             torch.cuda.empty_cache()
             out["decode"] = decode_bench(torch, peaks)
             out["scatter"] = scatter_bench(torch, peaks)
+            out["varlen"] = varlen_bench(args)
             out["cpu_baseline"] = cpu_baseline(torch)
+    llama = None
+    if not args.skip_extras and P == 8 and not args.no_llama:
+        # the end-to-end Llama-architecture configuration belongs to the 8-GPU line
+        try:
+            llama = e2e_llama(args, dist=dist, comm=comm, graph=True)
+        except Exception as e:                  # noqa: BLE001  (an extra must not lose the headline)
+            llama = {"error": f"{type(e).__name__}: {e}"}
+    if rank == 0:
+        if llama is not None:
+            out["e2e_llama"] = llama
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
         comm.close()
         dist.destroy_process_group()
+    if not all_ok:
+        sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -38,7 +38,8 @@ class ESPAttentionRuntime:
 
     def __init__(self, *, layers_num: int, q_head_num: int, kv_head_num: int, head_dim: int, max_total_token_num: int,
                  max_req_num: int, max_seq_length: int, sp_world_size: int = 1, total_rank: int = 0, sp_comm=None,
-                 dtype=torch.bfloat16, device="cuda", decode_block_seq: Optional[int] = None):
+                 dtype=torch.bfloat16, device="cuda", decode_block_seq: Optional[int] = None,
+                 peer_memory_decode="auto", peer_memory_max_batch: Optional[int] = None):
         self.layers_num = layers_num
         self.tp_q_head_num_ = q_head_num
         self.tp_k_head_num_ = kv_head_num
@@ -55,19 +56,66 @@ class ESPAttentionRuntime:
                                                   num_idle_slots=sp_world_size, device=device)
         self.req_manager = LongServeReqManager(max_req_num, max_seq_length, self.mem_manager)
         self._fused_groups = {}
+        # decode layer calls between two reads of the device status words (0 = never read them here)
+        self.status_check_interval = 32 * 64
+        self._decode_calls = 0
+        # Multi-master decode exchanges queries and partials over peer memory (NVLink stores and flags inside the kernels)
+        # whenever all instances sit in one node; the NCCL message exchange of the reference stays available
+        # (peer_memory_decode=False) and is what batches that do not span every instance use.
+        if peer_memory_decode == "auto":
+            peer_memory_decode = (sp_comm is not None and sp_world_size > 1 and self.device.type == "cuda"
+                                  and hasattr(sp_comm, "nccl_send") and torch.cuda.device_count() >= sp_world_size)
+        if peer_memory_decode and sp_world_size > 1:
+            mb = int(peer_memory_max_batch or min(max_req_num, 256))
+            for master in range(sp_world_size):
+                self.enable_peer_memory_decode(master, self._ring_all_gather_bytes, max_batch=mb)
 
     def enable_peer_memory_decode(self, master_rank: int, all_gather_bytes, max_batch: int):
         """Use NVLink stores and flags inside the kernels (``peer_decode.FusedDecodeGroup``) instead of NCCL messages
         for decode batches whose only master is ``master_rank`` and whose peers are all instances.  Collective:
         every instance must call it, with an ``all_gather_bytes`` that returns each rank's bytes in rank order."""
         from .peer_decode import FusedDecodeGroup
+        if master_rank in self._fused_groups:
+            self._fused_groups.pop(master_rank).close()
         self._fused_groups[master_rank] = FusedDecodeGroup(self.total_rank_, self.sp_world_size, master_rank, max_batch,
                                                            self.tp_q_head_num_, self.head_dim_, all_gather_bytes, self.dtype)
+
+    def _ring_all_gather_bytes(self, mine: bytes) -> List[bytes]:
+        """Every instance's 64 bytes in SP-rank order, passed round the ring of all instances over the communicator."""
+        P, rank = self.sp_world_size, self.total_rank_
+        assert len(mine) == 64
+        got = [None] * P
+        got[rank] = mine
+        cur = torch.tensor(list(mine), dtype=torch.uint8, device=self.device)
+        nxt, prv = (rank + 1) % P, (rank - 1 + P) % P
+        for i in range(1, P):
+            recv = torch.empty_like(cur)
+            self.sp_comm.wait_for_default_stream()
+            self.sp_comm.nccl_group_start()
+            self.sp_comm.nccl_recv(recv, prv)
+            self.sp_comm.nccl_send(cur, nxt)
+            self.sp_comm.nccl_group_end()
+            self.sp_comm.let_default_stream_wait()
+            got[(rank - i) % P] = bytes(recv.cpu().tolist())
+            cur = recv
+        return got
 
     def close(self):
         for g in self._fused_groups.values():
             g.close()
         self._fused_groups = {}
+
+    def check_device_status(self):
+        """Raise if a bounded in-kernel wait ran out, or a kernel met a slot id outside the pool, on this device since
+        the last check.  Synchronises the device: call it where the caller synchronises anyway (``token_attention`` does
+        every ``status_check_interval`` decode layers calls).  After a timed-out wait the gated kernels of the device
+        return at once and publish nothing until the status has been read here."""
+        st = ca.device_status()
+        dst = fd.device_status(clear=True)
+        kst = kv_ops.device_status(clear=True)
+        for name, v in (("prefill kernel", st), ("decode kernels / flag waits", dst), ("KV pool kernels", kst)):
+            if v[0] != 0:
+                raise RuntimeError(f"ESP attention device status, {name}: code {v[0]} ({tuple(v)})")
 
     # ------------------------------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -289,6 +337,10 @@ class ESPAttentionRuntime:
         """One layer's decode attention on this instance in its master and/or peer role
         (longserve_transformer_layer_infer.py:224-370).  Masters get the attention output, pure peers None."""
         pool_layer = self.mem_manager.kv_buffer[layer_idx]
+        self._decode_calls += 1
+        if (self.status_check_interval and self._decode_calls % self.status_check_interval == 0
+                and not torch.cuda.is_current_stream_capturing()):
+            self.check_device_status()
         single = st.peer_plan is None and (st.master_plan is None or len(st.master_plan.peers) == 1)
         if single and st.master_plan is not None:
             # the whole batch lives here: no exchange, stage 1 + merge only
@@ -310,18 +362,21 @@ class ESPAttentionRuntime:
                                                      fd.flash_decoding_stage1, fd.flash_decoding_stage2, out=out)
 
     def _fused_covers(self, st) -> bool:
-        """True when every master of this batch has a peer-memory group and the batch spans all instances
-        (the groups' layout assumes that)."""
+        """Whether this decode step goes over peer memory.  Decided from what EVERY instance of the batch knows -- the
+        batch's instance list, the masters named in the plans, and the groups that exist -- so that a master and its
+        peers always choose the same exchange: the batch must span all instances (the groups' layout assumes that) and
+        every master in sight must have a group."""
         if not self._fused_groups:
             return False
-        masters = []
+        peers = getattr(st, "logical_sp_peer_ranks", None)
+        if peers is None or sorted(peers) != list(range(self.sp_world_size)):
+            return False
+        masters = []          # (master rank, size of its mini-batch): both sides know both numbers
         if st.master_plan is not None:
-            if sorted(st.master_plan.peers) != list(range(self.sp_world_size)):
-                return False
-            masters.append(self.total_rank_)
+            masters.append((self.total_rank_, int(st.master_plan.b_seq_len.shape[0])))
         if st.peer_plan is not None:
-            masters += list(st.peer_plan.masters)
-        return bool(masters) and all(m in self._fused_groups for m in masters)
+            masters += [(m, b - a) for m, (a, b) in zip(st.peer_plan.masters, st.peer_plan.ranges)]
+        return bool(masters) and all(m in self._fused_groups and n <= self._fused_groups[m].B for m, n in masters)
 
     def _token_attention_peer_memory(self, qv, st, pool_layer, out):
         """The exchange of longserve_transformer_layer_infer.py:224-370 over peer memory: every master first pushes its
@@ -329,8 +384,11 @@ class ESPAttentionRuntime:
         order of ``peer_sp_master_rank_list``, then attends to its own tokens and merges."""
         rtt, Hkv = self.req_manager.req_to_token_indexs, self.tp_k_head_num_
         mp, pp = st.master_plan, st.peer_plan
+        # a group's step counter advances only when the group is really used this step, on the master (which always
+        # pushes) and on a peer (which serves unless the master's mini-batch is empty) alike: counters that drifted
+        # apart would let a stale flag satisfy a later wait
         groups = ([self._fused_groups[self.total_rank_]] if mp is not None else []) + \
-                 ([self._fused_groups[m] for m in pp.masters] if pp is not None else [])
+                 ([self._fused_groups[m] for m, (a, b) in zip(pp.masters, pp.ranges) if b > a] if pp is not None else [])
         for g in groups:
             g.next_step()
         if mp is not None:
@@ -367,6 +425,9 @@ class ESPAttentionRuntime:
         if total == 0:
             return
         if is_receiver:
+            # `buf` may be memory a kernel queued earlier on this stream still reads (the allocator hands a freed block
+            # back at once): the communicator's stream must not write into it before that kernel has finished
+            self.sp_comm.wait_for_default_stream()
             self.sp_comm.nccl_recv(buf, peer_sp_rank)
             alloc_mem = self.mem_manager.alloc(total)
             self.sp_comm.let_default_stream_wait()
@@ -378,6 +439,9 @@ class ESPAttentionRuntime:
                                                           max_migration_len)
             self.sp_comm.wait_for_default_stream()
             self.sp_comm.nccl_send(buf, peer_sp_rank)
+            # `buf` goes back to the allocator when this function returns: whatever reuses it on this stream has to wait
+            # for the send that still reads it (the reference fences here too, longserve_model.py:622)
+            self.sp_comm.let_default_stream_wait()
             # the kernel zeroed the device reference counts; tell the host allocator which slots those were
             # (a device->host read, acceptable here: migration is not on the per-step path)
             rt_, ids = self.req_manager.req_to_token_indexs, []

@@ -3,14 +3,21 @@
 //
 // One CTA owns 256 consecutive q rows of one (request, head) as two 128-row tiles.  Warp roles:
 //   warps 0-3  softmax of tile 0 (one thread per row), warps 4-7 softmax of tile 1,
-//   warp 8     TMA producer (Q tiles once, then K_0 V_0 K_1 V_1 ... through a ring of 32 KiB stages),
-//   warp 9     tcgen05.mma issuer and owner of the tensor-memory allocation; warps 10-11 only lend registers.
+//   warp 8     TMA producer (Q tiles once, then K_0, then the pairs {V_j, K_j+1} through two 64 KiB pair stages),
+//   warp 9     tcgen05.mma issuer (one thread) and owner of the tensor-memory allocation; warps 10-11 only lend registers.
 // Per kv tile and q tile:  S = Q K^T (tcgen05.mma, both operands K-major in 128B-swizzled smem, fp32
 // accumulator in tensor memory) -> softmax threads read their row with tcgen05.ld, apply the mask only
 // on diagonal/tail tiles, keep a running base-2 maximum with lazy rescaling of O, write P as packed
 // 16-bit back into the S columns -> O += P V (tcgen05.mma, A from tensor memory, V MN-major in smem).
 // The two q tiles ping-pong: while the tensor core runs tile 0's PV and next S, tile 1's softmax runs.
 // Tensor-memory map (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P aliases S.
+//
+// What bounds it.  The serial instruction stream of the one issuing thread is the critical path: a tcgen05.mma costs
+// that thread about 50 cycles to issue against 64 cycles of tensor-pipe time, so every wait, commit or spill reload in
+// its loop shows up as idle tensor pipe.  Hence: one wait and one commit per kv tile for the K/V data (pairs), a
+// register budget for the third warpgroup that keeps the issue loop out of local memory, no votes or warp barriers in
+// the loop, and a softmax that takes its exponentials against the running maximum without first waiting for the
+// tile's own maximum (so the two tiles' dependent chains stay shorter than the issuer's loop).
 //
 // Roofline: tensor-core bound; algorithmic FLOPs = 4 * D * (visible q,k pairs) per head.
 // Every mbarrier wait is bounded; on expiry the kernel records a status word and drains.
@@ -27,36 +34,25 @@ constexpr int BM = 128;               // rows per q tile
 constexpr int QT = 2;                 // q tiles per CTA
 constexpr int BN = 128;               // keys per kv tile
 constexpr int HD = 128;               // head dim
-constexpr int NSTAGE = 4;             // K/V ring stages
+constexpr int NSTAGE = 4;             // K/V tile slots in shared memory
 constexpr int TILE_BYTES = BN * HD * 2;
 constexpr int HALF_BYTES = TILE_BYTES / 2;   // 64 head-dim columns x 128 rows (one swizzle-128B panel)
-#ifndef ESP_PREFILL_THREADS
-#define ESP_PREFILL_THREADS 384       // 3 warpgroups: softmax tile 0, softmax tile 1, {producer, MMA, 2 idle warps}
-#endif
-#ifndef ESP_POLY_EXP_PER_32
-#define ESP_POLY_EXP_PER_32 0         // of every 32 exponentials, this many run on the FMA pipe instead of MUFU
-#endif
-constexpr int NUM_THREADS = ESP_PREFILL_THREADS;
-constexpr bool kUseSetMaxNReg = (NUM_THREADS == 384);
-constexpr int kPolyPer32 = ESP_POLY_EXP_PER_32;
-static_assert(kPolyPer32 == 0 || kPolyPer32 == 2 || kPolyPer32 == 4 || kPolyPer32 == 8 || kPolyPer32 == 16 || kPolyPer32 == 32,
-              "ESP_POLY_EXP_PER_32 must be 0 or a power of two up to 32");
+constexpr int NUM_THREADS = 384;      // 3 warpgroups: softmax tile 0, softmax tile 1, {producer, MMA issuer, 2 lenders}
 constexpr int TMEM_COLS = 512;
 constexpr float kRescaleThreshold = 8.0f;              // lazy O rescale: tolerate 2^8 growth
-#ifndef ESP_SPEC_MAX
-#define ESP_SPEC_MAX 0
-#endif
-constexpr bool kSpeculateMax = ESP_SPEC_MAX != 0;
-#ifndef ESP_CHEAP_DESC
-#define ESP_CHEAP_DESC 0
-#endif
-#ifndef ESP_WARP_ARRIVE
-#define ESP_WARP_ARRIVE 0
-#endif
-constexpr int kPReadyArrivals = ESP_WARP_ARRIVE ? 4 : 128;   // arrivals that publish one tile's P
+// setmaxnreg plan: the two softmax warpgroups raise their budget, the third warpgroup lowers it;
+// 256 * kRegsSoftmax + 128 * kRegsOther must fit the 384 * 168 registers the CTA is launched with.  Measured at 262144
+// tokens: (224, 56) 1049 TFLOP/s -- the issuing thread then spills inside its loop, which is the kernel's critical
+// path --, (216, 72) 1090, (208, 88) 1091 with the same code otherwise.
+constexpr int kRegsSoftmax = 216, kRegsOther = 72;
+static_assert(256 * kRegsSoftmax + 128 * kRegsOther <= 384 * 168 && kRegsSoftmax % 8 == 0 && kRegsOther % 8 == 0, "setmaxnreg plan");
+constexpr int kPReadyArrivals = 4;    // one arrival per softmax warp publishes a tile's P
 
-enum BarIdx { B_QFULL = 0, B_KVFULL = 2, B_KVEMPTY = 2 + NSTAGE, B_SFULL = 2 + 2 * NSTAGE,
-              B_PREADY = 4 + 2 * NSTAGE, B_ODONE = 6 + 2 * NSTAGE, B_COUNT = 8 + 2 * NSTAGE };
+// K/V tiles travel in pairs: after K_0 (which has barriers of its own), pair p = {V_p, K_p+1} is loaded under ONE
+// "full" barrier and released by ONE "empty" commit, so the issuing thread pays one wait and one commit per kv tile
+// instead of two of each.  Two pair stages; tile r of the sequence K_0 V_0 K_1 V_1 ... sits in slot r mod 4.
+enum BarIdx { B_QFULL = 0, B_K0FULL = 2, B_K0EMPTY = 3, B_PFULL = 4, B_PEMPTY = 6, B_SFULL = 8,
+              B_PREADY = 10, B_ODONE = 12, B_COUNT = 14 };
 
 constexpr int SMEM_Q = 0;
 constexpr int SMEM_KV = QT * TILE_BYTES;
@@ -69,14 +65,6 @@ __device__ int g_esp_status[4];
 // Bound of every mbarrier wait in SM cycles (about a second by default); esp_set_wait_limit_cycles changes it.
 __device__ long long g_wait_limit_cycles = 2000000000LL;
 
-#ifdef ESP_PREFILL_TRACE
-// Tuning aid, compiled only into experiment builds: per-phase SM clock stamps of one CTA.
-// g_trace[role][iteration][stamp]; role 0/1 = softmax tile 0/1 (lane 0 of its first warp), 2 = MMA issuer.
-__device__ long long g_trace[3][64][8];
-#define ESP_TRACE(role, j, k) do { if (trace_on && (j) < 64) g_trace[role][j][k] = clock64(); } while (0)
-#else
-#define ESP_TRACE(role, j, k) do { } while (0)
-#endif
 
 struct PrefillParams {
     void* o; float* m; float* l;
@@ -156,20 +144,6 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
-// 2^x on the FMA/ALU pipes for x <= ~8 (Cody-Waite split + degree-3 minimax polynomial on [0,1),
-// relative error < 1e-4, below the 16-bit rounding of P).  x is clamped at -126; -inf gives ~0 (2^-126 * p).
-__device__ __forceinline__ float exp2_poly(float x) {
-    x = fmaxf(x, -126.f);
-    float xf;
-    asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(xf) : "f"(x), "f"(12582912.f));   // 1.5 * 2^23: floor(x) lands in the mantissa
-    const float fl = xf - 12582912.f;
-    const float f = x - fl;                                                     // in [0, 1)
-    float pz = fmaf(f, 0.077119089663028717f, 0.227564394474029541f);
-    pz = fmaf(pz, f, 0.695146143436431885f);
-    pz = fmaf(pz, f, 1.0f);
-    return __uint_as_float(__float_as_uint(pz) + (__float_as_uint(xf) << 23));
-}
-
 // max over one 32-column chunk, optionally masked (columns > limit are invisible); four independent
 // chains keep the dependent latency off the critical path
 __device__ __forceinline__ float chunk_max(uint32_t (&r)[32], int col0, int limit, bool masked) {
@@ -189,63 +163,23 @@ __device__ __forceinline__ float chunk_max(uint32_t (&r)[32], int col0, int limi
     return fmaxf(fmax3(a[0], a[1], a[2]), a[3]);
 }
 
-// Packed version of exp2_poly for two values (f32x2 FMA-pipe instructions).
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-    x.x = fmaxf(x.x, -126.f); x.y = fmaxf(x.y, -126.f);
-    const float2 magic = make_float2(12582912.f, 12582912.f);
-    const float2 xf = __fadd2_rd(x, magic);                              // floor(x) in the mantissa
-    const float2 fl = __fadd2_rn(xf, make_float2(-12582912.f, -12582912.f));
-    const float2 f = __ffma2_rn(fl, make_float2(-1.f, -1.f), x);         // x - floor(x) in [0, 1)
-    float2 pz = __ffma2_rn(f, make_float2(0.077119089663028717f, 0.077119089663028717f),
-                           make_float2(0.227564394474029541f, 0.227564394474029541f));
-    pz = __ffma2_rn(pz, f, make_float2(0.695146143436431885f, 0.695146143436431885f));
-    pz = __ffma2_rn(pz, f, make_float2(1.f, 1.f));
-    return make_float2(__uint_as_float(__float_as_uint(pz.x) + (__float_as_uint(xf.x) << 23)),
-                       __uint_as_float(__float_as_uint(pz.y) + (__float_as_uint(xf.y) << 23)));
-}
-
-#ifndef ESP_EXP_VARIANT
-#define ESP_EXP_VARIANT 0
-#endif
 // p = 2^(s*scale - m) for one 32-column chunk; packs to 16-bit pairs and returns the chunk's row sum
-// (two independent packed accumulators)
+// (two independent packed accumulators).  With kTrackMax the chunk's raw maximum is folded into mx4 alongside
+// (ALU-pipe work that runs in the shadow of the exponentials).
 template <typename T, int OFF, bool kTrackMax = false>
 __device__ __forceinline__ float chunk_exp(const uint32_t (&r)[32], float scale, float neg_m, uint32_t (&pk)[32],
                                            float* mx4 = nullptr) {
     const float2 sc2 = make_float2(scale, scale), nm2 = make_float2(neg_m, neg_m);
     float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-    constexpr int kStride = kPolyPer32 > 0 ? 32 / kPolyPer32 : 1;   // every kStride-th pair goes to the FMA pipe
-#if ESP_EXP_VARIANT == 1
-    // staged: all scale/subtract first, then all exponentials, then sums and packing
-    float2 x[16], e[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-        x[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), sc2, nm2);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        if (kPolyPer32 > 0 && (i % kStride) == kStride - 1) e[i] = exp2_poly2(x[i]);
-        else { e[i].x = ex2(x[i].x); e[i].y = ex2(x[i].y); }
-    }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        acc[i & 1] = __fadd2_rn(acc[i & 1], e[i]);
-        pk[OFF + i] = Cvt<T>::pack(e[i].x, e[i].y);
-    }
-#else
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
         const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sc2, nm2);
         float2 e;
-        if (kPolyPer32 > 0 && ((i / 2) % kStride) == kStride - 1) {
-            e = exp2_poly2(x);
-        } else {
-            e.x = ex2(x.x); e.y = ex2(x.y);
-        }
+        e.x = ex2(x.x); e.y = ex2(x.y);
         acc[(i / 2) & 1] = __fadd2_rn(acc[(i / 2) & 1], e);
         pk[OFF + i / 2] = Cvt<T>::pack(e.x, e.y);
         if (kTrackMax) mx4[(i / 2) & 3] = fmax3(mx4[(i / 2) & 3], __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
     }
-#endif
     const float2 t = __fadd2_rn(acc[0], acc[1]);
     return t.x + t.y;
 }
@@ -265,9 +199,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
     volatile int* s_skip = reinterpret_cast<volatile int*>(smem_gen + SMEM_MISC + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef ESP_PREFILL_TRACE
-    const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == 9));
-#endif
     const int qb = p.num_qblocks - 1 - (int)blockIdx.x;      // heaviest q block first
     const int head = blockIdx.y, b = blockIdx.z;
     const int kvh = head / p.group;
@@ -318,7 +249,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
     // With 384 threads the third warpgroup (producer, MMA issuer, two idle warps) hands most of its
     // registers to the two softmax warpgroups; each role changes its budget at the top of its own branch.
     if (warp >= 8) {
-      if (kUseSetMaxNReg) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
       if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -331,46 +262,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                     tma_load_3d(dst + HALF_BYTES, &tm_q, bar(B_QFULL + t), 64, head, q_start + m0 + t * BM);
                 }
             }
-            for (int r = 0; r < 2 * nmax; ++r) {
-                const int stage = r % NSTAGE, use = r / NSTAGE;
-                if (use > 0 && !bounded_wait(bar(B_KVEMPTY + stage), (use - 1) & 1, s_abort, 1, r)) break;
-                const int j = r >> 1;
-                const CUtensorMap* tm = (r & 1) ? &tm_v : &tm_k;
-                const uint32_t dst = smem_base + SMEM_KV + stage * TILE_BYTES;
-                mbar_expect_tx(bar(B_KVFULL + stage), TILE_BYTES);
-                tma_load_3d(dst, tm, bar(B_KVFULL + stage), 0, kvh, kv_start + j * BN);
-                tma_load_3d(dst + HALF_BYTES, tm, bar(B_KVFULL + stage), 64, kvh, kv_start + j * BN);
+            auto load_tile = [&](const CUtensorMap* tm, int slot, int tile, uint32_t full_bar) {
+                const uint32_t dst = smem_base + SMEM_KV + slot * TILE_BYTES;
+                tma_load_3d(dst, tm, full_bar, 0, kvh, kv_start + tile * BN);
+                tma_load_3d(dst + HALF_BYTES, tm, full_bar, 64, kvh, kv_start + tile * BN);
+            };
+            mbar_expect_tx(bar(B_K0FULL), TILE_BYTES);
+            load_tile(&tm_k, 0, 0, bar(B_K0FULL));
+            for (int pr = 0; pr < nmax; ++pr) {
+                const int st = pr & 1;
+                // slots of pair stage 1 are {3, 0}: its first fill waits for K_0 to be consumed; later fills for the pair
+                // that used the stage before
+                if (pr == 1 && !bounded_wait(bar(B_K0EMPTY), 0, s_abort, 1, pr)) break;
+                if (pr >= 2 && !bounded_wait(bar(B_PEMPTY + st), ((pr >> 1) - 1) & 1, s_abort, 1, pr)) break;
+                const bool with_k = pr + 1 < nmax;
+                mbar_expect_tx(bar(B_PFULL + st), with_k ? 2 * TILE_BYTES : TILE_BYTES);
+                load_tile(&tm_v, (2 * pr + 1) & 3, pr, bar(B_PFULL + st));
+                if (with_k) load_tile(&tm_k, (2 * pr + 2) & 3, pr + 1, bar(B_PFULL + st));
             }
         }
       } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_s = make_idesc(Fmt<T>::kAB, 0, BM, BN);
         constexpr uint32_t idesc_pv = make_idesc(Fmt<T>::kAB, 1, BM, HD);
-#if ESP_CHEAP_DESC
-        // The issuing thread shares its scheduler with two softmax warps, so every instruction between two MMAs costs
-        // tensor-pipe time: descriptors are formed once per operand tile and stepped with one 64-bit add per MMA
-        // (the address field cannot carry out of its 14 bits: shared memory ends below 256 KiB).
-        const uint64_t dq0 = desc_kmajor_sw128(smem_base + SMEM_Q);
-        const uint64_t dk0 = desc_kmajor_sw128(smem_base + SMEM_KV);
-        const uint64_t dv0 = desc_mnmajor_sw128(smem_base + SMEM_KV, HALF_BYTES);
-        auto issue_s = [&](int t, int stage) {
-            const uint64_t qa = dq0 + (uint64_t)(t * (TILE_BYTES >> 4));
-            const uint64_t kb = dk0 + (uint64_t)(stage * (TILE_BYTES >> 4));
-            const uint32_t d = tmem_base + t * BN;
-#pragma unroll
-            for (int k = 0; k < HD / 16; ++k) {
-                const uint64_t off = (uint64_t)(((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4);
-                umma_ss(d, qa + off, kb + off, idesc_s, k > 0);
-            }
-        };
-        auto issue_pv = [&](int t, int stage, bool acc) {
-            const uint64_t vb = dv0 + (uint64_t)(stage * (TILE_BYTES >> 4));
-            const uint32_t d = tmem_base + QT * BN + t * HD, a = tmem_base + t * BN;
-#pragma unroll
-            for (int k = 0; k < BN / 16; ++k)
-                umma_ts(d, a + k * 8, vb + (uint64_t)(k * (2048 >> 4)), idesc_pv, (acc || k > 0) ? 1u : 0u);
-        };
-#else
         auto issue_s = [&](int t, int stage) {
             const uint32_t qa = smem_base + SMEM_Q + t * TILE_BYTES;
             const uint32_t kb = smem_base + SMEM_KV + stage * TILE_BYTES;
@@ -388,78 +302,59 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                         desc_mnmajor_sw128(vb + k * 2048, HALF_BYTES), idesc_pv, (acc || k > 0) ? 1u : 0u);
             }
         };
-#endif
-        bool ok = true;
+        // One thread runs the whole issue loop: no votes, no warp barriers, nothing but waits, MMAs and commits in its
+        // instruction stream (the loop of this thread is the kernel's critical path).
+        if (lane == 0) {
+            bool ok = true;
 #pragma unroll
-        for (int t = 0; t < QT; ++t)
-            if (n_tiles[t] > 0) ok = ok && bounded_wait(bar(B_QFULL + t), 0, s_abort, 2, t);
-        ok = ok && bounded_wait(bar(B_KVFULL + 0), 0, s_abort, 3, 0);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            tc_fence_after();
-            if (lane == 0) {
+            for (int t = 0; t < QT; ++t)
+                if (n_tiles[t] > 0) ok = ok && bounded_wait(bar(B_QFULL + t), 0, s_abort, 2, t);
+            ok = ok && bounded_wait(bar(B_K0FULL), 0, s_abort, 3, 0);
+            if (ok) {
+                tc_fence_after();
 #pragma unroll
                 for (int t = 0; t < QT; ++t)
                     if (n_tiles[t] > 0) { issue_s(t, 0); umma_commit(bar(B_SFULL + t)); }
-                umma_commit(bar(B_KVEMPTY + 0));
+                umma_commit(bar(B_K0EMPTY));
             }
             for (int j = 0; j < nmax && ok; ++j) {
-                const int rv = 2 * j + 1, sv = rv % NSTAGE;
-                ok = bounded_wait(bar(B_KVFULL + sv), (rv / NSTAGE) & 1, s_abort, 4, j);
-                ok = __all_sync(0xffffffffu, ok);
+                const int st = j & 1, sv = (2 * j + 1) & 3, sk = (2 * j + 2) & 3;
+                ok = bounded_wait(bar(B_PFULL + st), (j >> 1) & 1, s_abort, 4, j);      // V_j and K_j+1 have landed
                 if (!ok) break;
                 if ((j + 1) * BN > kv_len) {
                     // tail tile: rows past the request's last key may hold anything (even NaN); P is 0
                     // there, so make V finite by zeroing those rows in shared memory.
                     const int first_bad = kv_len - j * BN;
                     uint8_t* vs = smem_gen + SMEM_KV + sv * TILE_BYTES;
-                    for (int i = first_bad * 8 + lane; i < BN * 8; i += 32) {      // 8 x 16 B per 128 B row
+                    for (int i = first_bad * 8; i < BN * 8; ++i) {                 // 8 x 16 B per 128 B row
                         *reinterpret_cast<uint4*>(vs + i * 16) = make_uint4(0, 0, 0, 0);
                         *reinterpret_cast<uint4*>(vs + HALF_BYTES + i * 16) = make_uint4(0, 0, 0, 0);
                     }
                     fence_proxy_async_smem();
-                    __syncwarp();
-                }
-                const bool have_next = j + 1 < nmax;
-                const int rk = 2 * j + 2, sk = rk % NSTAGE;
-                if (have_next) {
-                    ok = bounded_wait(bar(B_KVFULL + sk), (rk / NSTAGE) & 1, s_abort, 5, j);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
                 }
 #pragma unroll
                 for (int t = 0; t < QT; ++t) {
                     if (j < n_tiles[t]) {
-                        ESP_TRACE(2, j, t * 4 + 0);
                         ok = bounded_wait(bar(B_PREADY + t), j & 1, s_abort, 6 + t, j);
-                        ESP_TRACE(2, j, t * 4 + 1);
-                        ok = __all_sync(0xffffffffu, ok);
                         if (!ok) break;
                         tc_fence_after();
-                        if (lane == 0) {
-                            issue_pv(t, sv, j > 0);
-                            ESP_TRACE(2, j, t * 4 + 2);
-                            if (j == n_tiles[t] - 1) umma_commit(bar(B_ODONE + t));
-                        }
+                        issue_pv(t, sv, j > 0);
+                        if (j == n_tiles[t] - 1) umma_commit(bar(B_ODONE + t));
                     }
-                    if (j + 1 < n_tiles[t] && lane == 0) {
+                    if (j + 1 < n_tiles[t]) {
                         issue_s(t, sk);
                         umma_commit(bar(B_SFULL + t));
-                        ESP_TRACE(2, j, t * 4 + 3);
                     }
                 }
                 if (!ok) break;
-                if (lane == 0) {
-                    umma_commit(bar(B_KVEMPTY + sv));
-                    if (have_next) umma_commit(bar(B_KVEMPTY + sk));
-                }
-                __syncwarp();
+                umma_commit(bar(B_PEMPTY + st));
             }
         }
+        __syncwarp();
       }
     } else {
         // ------------------------------------------------------------------ softmax + epilogue
-        if (kUseSetMaxNReg) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
         const int t = warp >> 2;                       // q tile of this warpgroup
         const int nt = n_tiles[t];
         if (nt > 0) {
@@ -472,9 +367,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
             float m_run = -INFINITY, l_run = 0.f;
             bool ok = true;
             for (int j = 0; j < nt; ++j) {
-                ESP_TRACE(t, j, 0);
                 ok = bounded_wait(bar(B_SFULL + t), j & 1, s_abort, 8 + t, j);
-                ESP_TRACE(t, j, 1);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
@@ -482,7 +375,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                 tmem_ld32(tS, sr[0]);
                 tmem_ld32(tS + 32, sr[1]);
                 tmem_wait_ld();
-                ESP_TRACE(t, j, 2);
                 tmem_ld32(tS + 64, sr[2]);          // second half streams in while the first is reduced
                 tmem_ld32(tS + 96, sr[3]);
                 const int n0 = j * BN;
@@ -496,8 +388,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                 // again and the tile is done the slow way: maximum first, O rescaled, then the exponentials.
                 float lsum = 0.f;
                 bool published = false;
-                if (kSpeculateMax && !masked && j > 0) {
-                    ESP_TRACE(t, j, 3);
+                if (!masked && j > 0) {
                     const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
                     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                     uint32_t pa[32], pb[32];
@@ -525,7 +416,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                     float mx = fmaxf(chunk_max(sr[0], 0, limit, masked), chunk_max(sr[1], 32, limit, masked));
                     tmem_wait_ld();
                     mx = fmax3(mx, chunk_max(sr[2], 64, limit, masked), chunk_max(sr[3], 96, limit, masked));
-                    ESP_TRACE(t, j, 3);
                     const float m_new = fmaxf(m_run, mx * scale);
                     // lazy rescale: keep the old reference maximum unless the row maximum grew by > 2^8
                     const bool need = (m_new > m_run + kRescaleThreshold) || (m_run == -INFINITY && m_new > -INFINITY);
@@ -562,17 +452,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                         lsum += s2 + s3;
                     }
                 }
-                ESP_TRACE(t, j, 4);
                 l_run += lsum;
                 tmem_wait_st();
                 tc_fence_before();
-#if ESP_WARP_ARRIVE
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_PREADY + t));
-#else
-                mbar_arrive(bar(B_PREADY + t));
-#endif
-                ESP_TRACE(t, j, 5);
             }
             if (ok) {
                 ok = bounded_wait(bar(B_ODONE + t), 0, s_abort, 10 + t, nt);
@@ -671,12 +555,12 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
                           const PrefillParams& pp, dim3 grid, cudaStream_t s) {
     // set on every launch: the attribute is per device and a process may drive several
     ESP_CUDA_TRY(cudaFuncSetAttribute(prefill_step_kernel<T, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
-    if (kUseSetMaxNReg) {
+    {
         // the in-kernel register re-distribution (256 softmax threads x 224 + 128 other threads x 56) must fit the
         // registers the CTA is launched with, or setmaxnreg.inc would block
         cudaFuncAttributes fa;
         ESP_CUDA_TRY(cudaFuncGetAttributes(&fa, prefill_step_kernel<T, OT>));
-        if (fa.numRegs * NUM_THREADS < 256 * 224 + 128 * 56) {
+        if (fa.numRegs * NUM_THREADS < 256 * kRegsSoftmax + 128 * kRegsOther) {
             snprintf(last_cuda_error_buf(), 256, "prefill kernel was built with %d registers per thread, too few for its setmaxnreg plan", fa.numRegs);
             return ESP_ERR_UNSUPPORTED;
         }
@@ -769,13 +653,6 @@ extern "C" int esp_prefill_lse(const float* m, const float* l, float* lse, int64
     return ESP_OK;
 }
 
-#ifdef ESP_PREFILL_TRACE
-extern "C" int esp_debug_read_trace(long long* out) {
-    ESP_CUDA_TRY(cudaDeviceSynchronize());
-    ESP_CUDA_TRY(cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 3 * 64 * 8));
-    return ESP_OK;
-}
-#endif
 
 extern "C" int esp_device_status(int32_t out[4], int32_t clear) {
     if (!out) return ESP_ERR_BAD_ARG;

@@ -27,17 +27,17 @@ def _copy2d(dst: int, dpitch: int, src: int, spitch: int, width: int, height: in
 class HostPrefillPipeline:
     """One instance's side of a ring prefill whose inputs and output are pinned host tensors.
 
-    ``metas`` / ``stride`` / ``peers`` / ``comm`` as for ``ring.ring_context_attention`` (``comm`` may be None for a ring of
-    one).  ``head_chunks`` must divide the number of KV heads.  Device scratch: two chunk-sized sets of q / kv / o / m / l
+    ``metas`` / ``stride`` / ``peers`` / ``comm`` / ``exchange`` as for ``ring.ring_context_attention`` (``comm`` may be None
+    for a ring of one or when ``exchange`` carries the blocks).  ``head_chunks`` must divide the number of KV heads.  Device scratch: two chunk-sized sets of q / kv / o / m / l
     and, for a ring of more than one instance, two chunk-sized receive buffers."""
 
     def __init__(self, q_tokens: int, max_token_num: int, num_q_heads: int, num_kv_heads: int, head_dim: int, *, rank: int,
                  peers: Sequence[int], metas: Sequence["ringmod.BlockMeta"], stride: int, max_len_in_batch: int, comm=None,
-                 head_chunks: int = 4, dtype=torch.bfloat16, device="cuda", overlap: bool = True):
+                 head_chunks: int = 8, dtype=torch.bfloat16, device="cuda", overlap: bool = True, exchange=None):
         assert num_q_heads % num_kv_heads == 0 and num_kv_heads % head_chunks == 0
         self.Tq, self.Tkv, self.Hq, self.Hkv, self.D = q_tokens, max_token_num, num_q_heads, num_kv_heads, head_dim
         self.rank, self.peers, self.metas, self.stride, self.comm = rank, list(peers), metas, stride, comm
-        self.max_len, self.overlap = max_len_in_batch, overlap
+        self.max_len, self.overlap, self.exchange = max_len_in_batch, overlap, exchange
         self.n = head_chunks
         self.kc = num_kv_heads // head_chunks                 # kv heads per chunk
         self.qc = self.kc * (num_q_heads // num_kv_heads)     # q heads per chunk
@@ -48,7 +48,8 @@ class HostPrefillPipeline:
         self.o = [torch.empty((q_tokens, self.qc, head_dim), dtype=dtype, device=dev) for _ in range(2)]
         self.m = [torch.empty((q_tokens, self.qc), dtype=torch.float32, device=dev) for _ in range(2)]
         self.l = [torch.empty((q_tokens, self.qc), dtype=torch.float32, device=dev) for _ in range(2)]
-        self.recv = [torch.empty_like(self.kv[0]) for _ in range(2)] if len(self.peers) > 1 else []
+        # with a copy-engine exchange the blocks arrive in the exchange's own buffers
+        self.recv = [torch.empty_like(self.kv[0]) for _ in range(2)] if (len(self.peers) > 1 and exchange is None) else []
         self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         self._ev = lambda: torch.cuda.Event()
         self._out_done: List[Optional[torch.cuda.Event]] = [None, None]     # o[b] has been copied out
@@ -99,7 +100,7 @@ class HostPrefillPipeline:
                 ringmod.ring_context_attention(q, kv, o, m, l, rank=self.rank, peers=self.peers, metas=self.metas, stride=self.stride,
                                                max_len_in_batch=self.max_len, num_kv_heads=self.kc, comm=self.comm,
                                                recv_buffers=self.recv, attention_fn=ca.context_attention_fwd,
-                                               init_fn=self._init_state, overlap=self.overlap)
+                                               init_fn=self._init_state, overlap=self.overlap, exchange=self.exchange)
             done = self._ev(); done.record(comp)
             self._comp_done[b] = done
             self.s_out.wait_event(done)

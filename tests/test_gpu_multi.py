@@ -27,7 +27,15 @@ def _setup(rank, world, port):
     return dist, rnccl.RNCCLComm(obj[0], world, rank)
 
 
-def _ring_worker(rank, world, port, striped, overlap, out):
+def _gather_over(dist, world):
+    def gather(b):
+        lst = [None] * world
+        dist.all_gather_object(lst, b)
+        return lst
+    return gather
+
+
+def _ring_worker(rank, world, port, striped, overlap, out, exchange_kind="nccl"):
     dist, comm = _setup(rank, world, port)
     from loongserve_b200 import context_attention as ca
     from loongserve_b200 import kv_ops, ring
@@ -56,14 +64,30 @@ def _ring_worker(rank, world, port, striped, overlap, out):
     keep = ring.KeepPlan(cb, ce, torch.randperm(T + 16, generator=gk)[:n_keep].to(dev), torch.arange(len(lens), dtype=torch.int32, device=dev),
                          torch.full((len(lens), 4000), O.INT32_MAX, dtype=torch.int32, device=dev),
                          torch.zeros(len(lens), dtype=torch.int32, device=dev))
+    exchange = None
+    if exchange_kind == "copy_engine":
+        # KV blocks travel as copy-engine transfers into the next instance's memory; a first pass without the
+        # bookkeeping leaves the flag counters at non-zero values for the pass that is checked
+        from loongserve_b200.peer_ring import CopyEngineRing
+        exchange = CopyEngineRing(rank, world, kv.numel() * kv.element_size(), _gather_over(dist, world), device=dev)
+        ring.ring_context_attention(qs, kv, o, m, l, rank=rank, peers=list(range(world)), metas=metas, stride=stride,
+                                    max_len_in_batch=max(local_len[rank]), num_kv_heads=Hkv, comm=None, recv_buffers=None,
+                                    attention_fn=ca.context_attention_fwd, init_fn=ca.init_attention_state, exchange=exchange)
+        o.fill_(float("nan"))
     ring.ring_context_attention(qs, kv, o, m, l, rank=rank, peers=list(range(world)), metas=metas, stride=stride,
                                 max_len_in_batch=max(local_len[rank]), num_kv_heads=Hkv, comm=comm,
                                 recv_buffers=[torch.empty_like(kv), torch.empty_like(kv)],
                                 attention_fn=ca.context_attention_fwd, init_fn=ca.init_attention_state, overlap=overlap,
                                 keep=keep if striped else None, pool_layer=pool, layer_idx=0,
-                                keep_fns=(kv_ops.pre_copy_and_register_kv, kv_ops.destindex_copy_and_register_kv))
+                                keep_fns=(kv_ops.pre_copy_and_register_kv, kv_ops.destindex_copy_and_register_kv),
+                                exchange=exchange)
     torch.cuda.synchronize()
     st = ca.device_status()
+    if exchange is not None:
+        exchange.check()                      # no flag wait ran out
+        assert exchange.sent[(rank + 1) % world] == exchange.received[(rank - 1) % world] == 2 * (world - 1)
+        dist.barrier()
+        exchange.close()
     torch.save(dict(o=o.cpu(), lse=ca.attention_lse(m, l).cpu(), status=st, pool=pool.cpu(), rtt=keep.req_to_token_indexs.cpu(),
                     cb=cb.cpu(), ce=ce.cpu()), os.path.join(out, f"r{rank}.pt"))
     dist.barrier()
@@ -71,12 +95,13 @@ def _ring_worker(rank, world, port, striped, overlap, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("striped,overlap", [(True, True), (False, True), (True, False)])
-def test_ring_two_gpus(tmp_path, striped, overlap):
+@pytest.mark.parametrize("striped,overlap,exchange_kind", [(True, True, "nccl"), (False, True, "nccl"), (True, False, "nccl"),
+                                                          (True, True, "copy_engine"), (False, True, "copy_engine")])
+def test_ring_two_gpus(tmp_path, striped, overlap, exchange_kind):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     world = 2
-    mp.spawn(_ring_worker, args=(world, _free_port(), striped, overlap, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_ring_worker, args=(world, _free_port(), striped, overlap, str(tmp_path), exchange_kind), nprocs=world, join=True)
     g = torch.Generator().manual_seed(0)
     lens = [3000, 77, 1025]
     T, Hq, Hkv, D = sum(lens), 8, 4, 128
@@ -174,7 +199,7 @@ def _runtime_worker(rank, world, port, out):
     L, Hq, Hkv, D = 2, 8, 4, 128
     rt = ESPAttentionRuntime(layers_num=L, q_head_num=Hq, kv_head_num=Hkv, head_dim=D, max_total_token_num=4096, max_req_num=8,
                              max_seq_length=4096, sp_world_size=world, total_rank=rank, sp_comm=comm, dtype=torch.bfloat16,
-                             device=dev)
+                             device=dev, peer_memory_decode=False)
     g = torch.Generator().manual_seed(33)
     lens = [1500, 64, 777]
     B, T = len(lens), sum(lens)
@@ -216,7 +241,7 @@ def _runtime_worker(rank, world, port, out):
                              peer_b_req_idx=b_req, peer_b_seq_len=k_len, peer_max_len_in_batch=max(kept), block_seq=bs,
                              peer_mid_o=torch.empty(nblk, B, Hq, D, **f32), peer_mid_lse=torch.empty(nblk, B, Hq, **f32),
                              peer_o=torch.empty(B, Hq, D, **f32), peer_lse=torch.empty(B, Hq, **f32))
-    dstate = LongServeState(master_plan=master, peer_plan=peer)
+    dstate = LongServeState(master_plan=master, peer_plan=peer, logical_sp_peer_ranks=list(range(world)))
     dec1 = [rt.token_attention(qd[layer].to(dev) if rank == 0 else None, dstate, layer) for layer in range(L)]
     # ---- decode-stage migration: instance 1 hands the last 100 / 0 / 50 kept tokens of each request to instance 0
     mig = torch.tensor([100, 0, 50], dtype=torch.int32, device=dev)
@@ -255,8 +280,8 @@ def _runtime_worker(rank, world, port, out):
 
 
 class LongServeState:
-    def __init__(self, master_plan, peer_plan):
-        self.master_plan, self.peer_plan = master_plan, peer_plan
+    def __init__(self, master_plan, peer_plan, logical_sp_peer_ranks=None):
+        self.master_plan, self.peer_plan, self.logical_sp_peer_ranks = master_plan, peer_plan, logical_sp_peer_ranks
 
 
 def test_runtime_prefill_keep_decode_migrate_two_gpus(tmp_path):
@@ -299,7 +324,8 @@ def _two_masters_worker(rank, world, port, out, peer_memory=False):
     dev = torch.device("cuda", rank)
     Hq, Hkv, D = 8, 2, 128
     rt = ESPAttentionRuntime(layers_num=1, q_head_num=Hq, kv_head_num=Hkv, head_dim=D, max_total_token_num=8192, max_req_num=16,
-                             max_seq_length=4096, sp_world_size=world, total_rank=rank, sp_comm=comm, dtype=torch.float16, device=dev)
+                             max_seq_length=4096, sp_world_size=world, total_rank=rank, sp_comm=comm, dtype=torch.float16, device=dev,
+                             peer_memory_decode=False)
     if peer_memory:
         def gather(b):
             lst = [None] * world
@@ -475,7 +501,9 @@ def _forward_kwargs_worker(rank, world, port, out):
     dec_logits = stack.forward(**dk)
     torch.cuda.synchronize()
     torch.save(dict(pre=pre_logits.cpu(), dec=None if dec_logits is None else dec_logits.cpu()), os.path.join(out, f"fw{rank}.pt"))
+    rt.check_device_status()
     dist.barrier()
+    rt.close()
     comm.close()
     dist.destroy_process_group()
 
@@ -590,7 +618,7 @@ def test_graphed_decode_matches_kernel_by_kernel_decode_two_gpus(tmp_path):
                 assert bool(((a - b).abs() <= 1e-3 + 1e-3 * a.abs()).all()), (a - b).abs().max()
 
 
-def _host_pipeline_worker(rank, world, port, out):
+def _host_pipeline_worker(rank, world, port, out, exchange_kind="nccl"):
     """Ring prefill from pinned host buffers, pipelined over chunks of heads, against the plain device-resident ring."""
     dist, comm = _setup(rank, world, port)
     from loongserve_b200 import context_attention as ca
@@ -612,8 +640,12 @@ def _host_pipeline_worker(rank, world, port, out):
     hkv = hkv.pin_memory()
     ho = torch.zeros_like(hq).pin_memory()
     metas = [ring.BlockMeta.from_lengths(local_len[r], first[r], dev) for r in range(world)]
+    exchange = None
+    if exchange_kind == "copy_engine":
+        from loongserve_b200.peer_ring import CopyEngineRing
+        exchange = CopyEngineRing(rank, world, hkv.numel() * 2, _gather_over(dist, world), device=dev)
     pipe = HostPrefillPipeline(hq.shape[0], max_tok, Hq, Hkv, D, rank=rank, peers=list(range(world)), metas=metas, stride=stride,
-                               max_len_in_batch=max(local_len[rank]), comm=comm, head_chunks=2, device=dev)
+                               max_len_in_batch=max(local_len[rank]), comm=comm, head_chunks=2, device=dev, exchange=exchange)
     pipe.run(hq, hkv, ho).synchronize()
     ho.zero_()
     pipe.run(hq, hkv, ho).synchronize()
@@ -626,16 +658,21 @@ def _host_pipeline_worker(rank, world, port, out):
     torch.cuda.synchronize()
     torch.save(dict(same=bool(torch.equal(ho.view(torch.int16), o.cpu().view(torch.int16))), o=ho.clone(), status=ca.device_status()),
                os.path.join(out, f"hp{rank}.pt"))
+    if exchange is not None:
+        exchange.check()
+        dist.barrier()
+        exchange.close()
     dist.barrier()
     comm.close()
     dist.destroy_process_group()
 
 
-def test_host_pipeline_ring_two_gpus(tmp_path):
+@pytest.mark.parametrize("exchange_kind", ["nccl", "copy_engine"])
+def test_host_pipeline_ring_two_gpus(tmp_path, exchange_kind):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     world = 2
-    mp.spawn(_host_pipeline_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_host_pipeline_worker, args=(world, _free_port(), str(tmp_path), exchange_kind), nprocs=world, join=True)
     g = torch.Generator().manual_seed(3)
     lens = [1500, 130]
     T, Hq, Hkv, D = sum(lens), 8, 4, 128
@@ -647,3 +684,64 @@ def test_host_pipeline_ring_two_gpus(tmp_path):
     assert all(p["same"] and p["status"][0] == 0 for p in parts)
     o = O.unshard_tokens([p["o"] for p in parts], lens, world, True)
     assert bool(((o.float() - ro).abs() <= 2e-2 + 1e-2 * ro.abs()).all())
+
+
+def _migrate_chunked_worker(rank, world, port, out):
+    """Instance 1 hands the tail of three requests to instance 0 in chunks of at most 700 tokens: five chunks of about
+    3 MB each, back to back, every one through a freshly allocated staging buffer -- the allocator gives each chunk the
+    block the previous one just released, so a missing fence between the exchange stream and the kernels shows up as
+    corrupted rows."""
+    dist, comm = _setup(rank, world, port)
+    from loongserve_b200.attention_runtime import ESPAttentionRuntime
+    dev = torch.device("cuda", rank)
+    L, Hkv, D = 4, 4, 128
+    rt = ESPAttentionRuntime(layers_num=L, q_head_num=4, kv_head_num=Hkv, head_dim=D, max_total_token_num=8192, max_req_num=8,
+                             max_seq_length=8192, sp_world_size=world, total_rank=rank, sp_comm=comm, dtype=torch.bfloat16,
+                             device=dev, peer_memory_decode=False)
+    lens = [1800, 900, 1200]                      # tokens instance 1 holds of each request; instance 0 holds 5 of each
+    mig = [1500, 700, 1000]
+    g = torch.Generator().manual_seed(11)
+    rows = [torch.randn(L, n, 2 * Hkv, D, generator=g).to(torch.bfloat16) for n in lens]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    have = lens if rank == 1 else [5, 5, 5]
+    for b, n in enumerate(have):
+        slots = rt.mem_manager.alloc(n)
+        rt.req_manager.req_to_token_indexs[b, :n] = slots.to(torch.int32)
+        if rank == 1:
+            rt.mem_manager.kv_buffer[:, slots] = rows[b].to(dev)
+    torch.cuda.synchronize(); dist.barrier()
+    new_len = rt.migrate_chunked(rank == 0, [0, 1, 2], mig, have, 1 - rank, max_mig_len=700)
+    torch.cuda.synchronize()
+    res = dict(new_len=new_len, free=rt.mem_manager.can_use_mem_size, state_sum=int(rt.mem_manager.mem_state.sum()))
+    if rank == 0:
+        got = []
+        for b in range(3):
+            slots = rt.req_manager.req_to_token_indexs[b, 5:5 + mig[b]].long()
+            got.append(rt.mem_manager.kv_buffer[:, slots].cpu())
+        res["got"] = got
+    torch.save(res, os.path.join(out, f"mc{rank}.pt"))
+    rt.check_device_status()
+    dist.barrier()
+    rt.close()
+    comm.close()
+    dist.destroy_process_group()
+
+
+def test_migrate_chunked_many_chunks_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mp.spawn(_migrate_chunked_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    r0 = torch.load(os.path.join(str(tmp_path), "mc0.pt")); r1 = torch.load(os.path.join(str(tmp_path), "mc1.pt"))
+    lens, mig, L, Hkv, D = [1800, 900, 1200], [1500, 700, 1000], 4, 4, 128
+    g = torch.Generator().manual_seed(11)
+    rows = [torch.randn(L, n, 2 * Hkv, D, generator=g).to(torch.bfloat16) for n in lens]
+    assert r0["new_len"] == [5 + m for m in mig] and r1["new_len"] == [n - m for n, m in zip(lens, mig)]
+    assert r0["free"] == 8192 - 15 - sum(mig) and r1["free"] == 8192 - sum(lens) + sum(mig)
+    assert r0["state_sum"] == 15 + sum(mig) and r1["state_sum"] == sum(lens) - sum(mig)
+    # the receiver appended every request's migrated rows in their original order, bit for bit; chunks were cut from the
+    # END of the request list, and each chunk takes the LAST tokens still held by the sender
+    for b in range(3):
+        want = rows[b][:, lens[b] - mig[b]:]
+        got = r0["got"][b]
+        key = lambda t: sorted(map(bytes, t.permute(1, 0, 2, 3).reshape(t.shape[1], -1).contiguous().view(torch.uint8).numpy()))
+        assert key(got) == key(want), f"request {b}: migrated rows differ from the sender's originals"

@@ -266,6 +266,50 @@ def test_pool_manager_duplicates_resize_and_over_release():
     assert rm.can_use_req_size == 4 and not rm.req_state.any()
 
 
+def test_master_and_peers_choose_the_same_decode_exchange():
+    """Peer-memory decode is chosen from data every instance of a batch has, so a master and its peers agree: a batch
+    over a subset of the instances goes over NCCL on all of them, one over all instances over peer memory on all of them;
+    and a peer advances the step counter of a master's group only when it really serves that master."""
+    from types import SimpleNamespace as NS
+    from loongserve_b200.attention_runtime import ESPAttentionRuntime
+
+    def runtime(rank):
+        rt = ESPAttentionRuntime(layers_num=1, q_head_num=2, kv_head_num=2, head_dim=128, max_total_token_num=16, max_req_num=2,
+                                 max_seq_length=8, sp_world_size=4, total_rank=rank, dtype=torch.float16, device="cpu")
+        rt._fused_groups = {0: NS(B=8), 2: NS(B=8)}
+        return rt
+
+    i32 = lambda n: torch.zeros(n, dtype=torch.int32)
+    master_plan = NS(peers=[0, 1], b_seq_len=i32(3))
+    peer_plan = NS(masters=[0], ranges=[(0, 3)])
+    # batch on instances {0, 1} only: master 0 and peer 1 must both fall back to the NCCL exchange
+    assert runtime(0)._fused_covers(NS(master_plan=master_plan, peer_plan=None, logical_sp_peer_ranks=[0, 1])) is False
+    assert runtime(1)._fused_covers(NS(master_plan=None, peer_plan=peer_plan, logical_sp_peer_ranks=[0, 1])) is False
+    # batch on all four instances, masters 0 and 2 both have groups
+    full = [0, 1, 2, 3]
+    assert runtime(0)._fused_covers(NS(master_plan=NS(peers=full, b_seq_len=i32(3)), peer_plan=NS(masters=[2], ranges=[(0, 1)]), logical_sp_peer_ranks=full))
+    assert runtime(3)._fused_covers(NS(master_plan=None, peer_plan=NS(masters=[0, 2], ranges=[(0, 3), (3, 4)]), logical_sp_peer_ranks=full))
+    # a master without a group: NCCL everywhere
+    assert not runtime(3)._fused_covers(NS(master_plan=None, peer_plan=NS(masters=[0, 1], ranges=[(0, 3), (3, 4)]), logical_sp_peer_ranks=full))
+    assert not runtime(1)._fused_covers(NS(master_plan=NS(peers=full, b_seq_len=i32(3)), peer_plan=None, logical_sp_peer_ranks=full))
+    # a mini-batch larger than the group was sized for: NCCL on the master and on the peers alike
+    assert not runtime(0)._fused_covers(NS(master_plan=NS(peers=full, b_seq_len=i32(9)), peer_plan=None, logical_sp_peer_ranks=full))
+    assert not runtime(3)._fused_covers(NS(master_plan=None, peer_plan=NS(masters=[0], ranges=[(0, 9)]), logical_sp_peer_ranks=full))
+
+    # step counters: the peer skips a master whose mini-batch is empty, as that master's own group does not advance either
+    class G:
+        def __init__(self): self.steps, self.served = 0, 0
+        def next_step(self): self.steps += 1
+        def peer_serve(self, *a, **k): self.served += 1
+    rt = runtime(3)
+    rt._fused_groups = {0: G(), 2: G()}
+    pp = NS(masters=[0, 2], ranges=[(0, 2), (2, 2)], peer_max_len_in_batch=4, block_seq=4, peer_mid_o=torch.zeros(1, 2, 2, 128),
+            peer_mid_lse=torch.zeros(1, 2, 2), peer_b_req_idx=torch.zeros(2, dtype=torch.int32), peer_b_seq_len=torch.ones(2, dtype=torch.int32))
+    rt._token_attention_peer_memory(None, NS(master_plan=None, peer_plan=pp), rt.mem_manager.kv_buffer[0], None)
+    assert (rt._fused_groups[0].steps, rt._fused_groups[0].served) == (1, 1)
+    assert (rt._fused_groups[2].steps, rt._fused_groups[2].served) == (0, 0)
+
+
 def test_migration_chunker_order_and_bookkeeping():
     """The chunker takes requests from the end of the lists, splits at the buffer size and re-queues the rest, and
     adjusts the local lengths, as the reference's worker shell does (model_rpc.py:178-217)."""
