@@ -29,6 +29,15 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC", "-cudart", "shared"]
 
 
+def reference_dir():
+    """A checkout of the reference project, for the builds and tests that compare against it: the directory named by
+    ESP_REFERENCE_DIR, else a sibling directory `reference` next to this repository.  None when neither exists."""
+    for cand in (os.environ.get("ESP_REFERENCE_DIR"), os.path.join(os.path.dirname(ROOT), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "loongserve")):
+            return os.path.abspath(cand)
+    return None
+
+
 def _nvcc() -> str:
     for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and os.path.exists(cand):

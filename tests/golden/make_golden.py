@@ -25,8 +25,13 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
 OUT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(OUT)))
+from loongserve_b200.build import reference_dir  # noqa: E402
+
+REF = sys.argv[1] if len(sys.argv) > 1 else reference_dir()
+if REF is None:
+    sys.exit("usage: make_golden.py /path/to/reference   (or set ESP_REFERENCE_DIR)")
 
 
 def load(name, rel):

@@ -78,9 +78,10 @@ def test_unmodified_reference_modules_import_against_this_package():
     and bind this package's kernels.  The checkout must be importable BEFORE install() so that its real parent packages
     are used."""
     import os
-    ref = os.environ.get("ESP_REFERENCE_DIR", "/root/reference")
-    if not os.path.isdir(os.path.join(ref, "loongserve", "models", "llama")):
-        pytest.skip("reference checkout not present")
+    from loongserve_b200.build import reference_dir
+    ref = reference_dir()
+    if ref is None or not os.path.isdir(os.path.join(ref, "loongserve", "models", "llama")):
+        pytest.skip("reference checkout not present (set ESP_REFERENCE_DIR)")
     before = set(sys.modules)
     sys.path.insert(0, ref)
     try:

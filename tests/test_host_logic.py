@@ -1,6 +1,6 @@
 """Host-side logic on CPU: the pool managers against the reference-generated golden trace, and the ring /
 multi-master orchestration run as world_size-2 gloo processes with the CPU oracle standing in for the
-kernels (BASELINE correctness configuration: one 4096-token sequence, 2 contiguous shards of 2048,
+kernels (the correctness configuration that needs no GPU: one 4096-token sequence, 2 contiguous shards of 2048,
 32 q/kv heads x 128, fp32, seed 0)."""
 import os
 import socket

@@ -9,13 +9,14 @@ import pytest
 import torch
 
 from loongserve_b200 import dropin, mem_manager, rnccl
+from loongserve_b200.build import reference_dir
 
-REF = os.environ.get("ESP_REFERENCE_DIR", "/root/reference")
+REF = reference_dir() or ""
 FILES = ["loongserve/models/llama/layer_infer/longserve_transformer_layer_infer.py", "loongserve/models/llama/longserve_model.py",
          "loongserve/longserve_server/router/manager.py", "loongserve/longserve_server/router/model_infer/model_rpc.py"]
 
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "loongserve", "models", "llama")),
-                                reason="reference checkout not present")
+                                reason="reference checkout not present (set ESP_REFERENCE_DIR)")
 
 
 def _trees():
