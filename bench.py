@@ -999,11 +999,21 @@ def main():
             out["cpu_baseline"] = cpu_baseline(torch)
     llama = None
     if not args.skip_extras and P == 8 and not args.no_llama:
-        # the end-to-end Llama-architecture configuration belongs to the 8-GPU line
+        # the end-to-end Llama-architecture configuration belongs to the 8-GPU line.  It is an extra: neither an exception
+        # nor a stall in it may lose the headline, so a watchdog prints the line without it after ten minutes.
+        def give_up():
+            if rank == 0:
+                out["e2e_llama"] = {"error": "did not finish within 600 s"}
+                print(json.dumps(out), flush=True)
+            os._exit(0 if all_ok else 3)
+        dog = threading.Timer(600.0, give_up)
+        dog.daemon = True
+        dog.start()
         try:
             llama = e2e_llama(args, dist=dist, comm=comm, graph=True)
-        except Exception as e:                  # noqa: BLE001  (an extra must not lose the headline)
+        except Exception as e:                  # noqa: BLE001
             llama = {"error": f"{type(e).__name__}: {e}"}
+        dog.cancel()
     if rank == 0:
         if llama is not None:
             out["e2e_llama"] = llama
