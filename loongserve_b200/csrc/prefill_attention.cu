@@ -22,6 +22,7 @@
 // Roofline: tensor-core bound; algorithmic FLOPs = 4 * D * (visible q,k pairs) per head.
 // Every mbarrier wait is bounded; on expiry the kernel records a status word and drains.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "esp_common.cuh"
 #include "sm100_ptx.cuh"
@@ -40,6 +41,7 @@ constexpr int HALF_BYTES = TILE_BYTES / 2;   // 64 head-dim columns x 128 rows (
 constexpr int NUM_THREADS = 384;      // 3 warpgroups: softmax tile 0, softmax tile 1, {producer, MMA issuer, 2 lenders}
 constexpr int TMEM_COLS = 512;
 constexpr float kRescaleThreshold = 8.0f;              // lazy O rescale: tolerate 2^8 growth
+constexpr float kSpecSumLimit = 256.0f;                // 2^kRescaleThreshold
 // setmaxnreg plan: the two softmax warpgroups raise their budget, the third warpgroup lowers it;
 // 256 * kRegsSoftmax + 128 * kRegsOther must fit the 384 * 168 registers the CTA is launched with.  Measured at 262144
 // tokens: (224, 56) 1049 TFLOP/s -- the issuing thread then spills inside its loop, which is the kernel's critical
@@ -164,11 +166,9 @@ __device__ __forceinline__ float chunk_max(uint32_t (&r)[32], int col0, int limi
 }
 
 // p = 2^(s*scale - m) for one 32-column chunk; packs to 16-bit pairs and returns the chunk's row sum
-// (two independent packed accumulators).  With kTrackMax the chunk's raw maximum is folded into mx4 alongside
-// (ALU-pipe work that runs in the shadow of the exponentials).
-template <typename T, int OFF, bool kTrackMax = false>
-__device__ __forceinline__ float chunk_exp(const uint32_t (&r)[32], float scale, float neg_m, uint32_t (&pk)[32],
-                                           float* mx4 = nullptr) {
+// (two independent packed accumulators).
+template <typename T, int OFF>
+__device__ __forceinline__ float chunk_exp(const uint32_t (&r)[32], float scale, float neg_m, uint32_t (&pk)[32]) {
     const float2 sc2 = make_float2(scale, scale), nm2 = make_float2(neg_m, neg_m);
     float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
@@ -178,7 +178,6 @@ __device__ __forceinline__ float chunk_exp(const uint32_t (&r)[32], float scale,
         e.x = ex2(x.x); e.y = ex2(x.y);
         acc[(i / 2) & 1] = __fadd2_rn(acc[(i / 2) & 1], e);
         pk[OFF + i / 2] = Cvt<T>::pack(e.x, e.y);
-        if (kTrackMax) mx4[(i / 2) & 3] = fmax3(mx4[(i / 2) & 3], __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
     }
     const float2 t = __fadd2_rn(acc[0], acc[1]);
     return t.x + t.y;
@@ -382,27 +381,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                 const bool masked = (n0 + BN - 1 > r0 - delta) || (n0 + BN > kv_len);
                 const int limit = min(row - delta, kv_len - 1) - n0;     // columns <= limit are visible
                 // After the first tile the running maximum rarely grows by more than the lazy-rescale threshold, so the
-                // exponentials of an unmasked tile are taken against the running maximum straight away while the
-                // tile's own maximum is found alongside on the ALU pipe.  P is stored only once every row of the warp
-                // is known to have stayed within the threshold; otherwise S (still intact in tensor memory) is read
-                // again and the tile is done the slow way: maximum first, O rescaled, then the exponentials.
+                // exponentials of an unmasked tile are taken against the running maximum straight away, without looking
+                // for the tile's own maximum (every instruction of this loop counts: the softmax warps' instruction
+                // stream, with the issuing thread's, is what bounds the kernel).  P is stored only once every row of
+                // the warp is known to have stayed within the threshold -- its row sum proves it; otherwise S (still
+                // intact in tensor memory) is read again and the tile is done the slow way: maximum first, O rescaled,
+                // then the exponentials.
                 float lsum = 0.f;
                 bool published = false;
                 if (!masked && j > 0) {
                     const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
-                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                     uint32_t pa[32], pb[32];
-                    const float s0 = chunk_exp<T, 0, true>(sr[0], scale, neg_m, pa, mx4);
-                    const float s1 = chunk_exp<T, 16, true>(sr[1], scale, neg_m, pa, mx4);
+                    const float s0 = chunk_exp<T, 0>(sr[0], scale, neg_m, pa);
+                    const float s1 = chunk_exp<T, 16>(sr[1], scale, neg_m, pa);
                     tmem_wait_ld();
-                    const float s2 = chunk_exp<T, 0, true>(sr[2], scale, neg_m, pb, mx4);
-                    const float s3 = chunk_exp<T, 16, true>(sr[3], scale, neg_m, pb, mx4);
-                    const float m_tile = fmaxf(fmax3(mx4[0], mx4[1], mx4[2]), mx4[3]) * scale;
-                    const bool outgrown = (m_tile > m_run + kRescaleThreshold) || (m_run == -INFINITY);
+                    const float s2 = chunk_exp<T, 0>(sr[2], scale, neg_m, pb);
+                    const float s3 = chunk_exp<T, 16>(sr[3], scale, neg_m, pb);
+                    lsum = (s0 + s1) + (s2 + s3);
+                    // no exponential can exceed the row's sum of them: a sum within 2^threshold proves that the tile's maximum
+                    // stayed within the threshold (a larger sum, an infinity or a NaN sends the tile down the exact path)
+                    const bool outgrown = !(lsum <= kSpecSumLimit) || (m_run == -INFINITY);
                     if (!__any_sync(0xffffffffu, outgrown)) {
                         tmem_st32(tS, pa);
                         tmem_st32(tS + 32, pb);
-                        lsum = (s0 + s1) + (s2 + s3);
                         published = true;
                     } else {
                         tmem_ld32(tS, sr[0]);
@@ -512,6 +513,365 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
 }
 
 // ------------------------------------------------------------------------------------------------
+// The same step for CTA PAIRS (cluster of two, tcgen05 cta_group::2): a pair owns 512 consecutive q rows, CTA c of the pair the
+// rows [256 c, 256 c + 256) as its two 128-row tiles.  Tile t of both CTAs forms one 256-row "slot": ONE thread of the even CTA
+// issues M = 256 MMAs that run on both SMs, each CTA supplying its own Q rows / its own P (tensor memory) and HALF of the K tile
+// (64 keys) or of the V tile (64 head dims) from its own shared memory.  So every MMA instruction does twice the work -- the
+// issuing thread's instruction stream, the bound of the single-CTA kernel, is halved per FLOP -- and each SM reads half of B.
+// Every CTA fetches its own halves with plain TMA loads (no multicast); loads of both CTAs are counted on barriers in the even
+// CTA, where the issuing thread waits; tcgen05.commit arrives on the barriers of both CTAs.  K_0 has a buffer of its own, the
+// pairs {V_j, K_j+1} go through four 32 KiB stages per CTA.
+constexpr int NPS = 4;                                  // pair stages
+constexpr int HALF_TILE = TILE_BYTES / 2;               // 16 KiB: 64 keys x 128 dims of K, or 128 keys x 64 dims of V
+enum PairBar { PB_QFULL = 0, PB_K0FULL = 2, PB_PFULL = 3, PB_PEMPTY = 3 + NPS, PB_SFULL = 3 + 2 * NPS, PB_PREADY = 5 + 2 * NPS,
+               PB_ODONE = 7 + 2 * NPS, PB_VREQ = 9 + 2 * NPS, PB_VCLEAN = 10 + 2 * NPS, PB_COUNT = 11 + 2 * NPS };
+constexpr int PSMEM_Q = 0;
+constexpr int PSMEM_K0 = QT * TILE_BYTES;
+constexpr int PSMEM_PAIR = PSMEM_K0 + HALF_TILE;        // stage s: V half at +s*32 KiB, K half 16 KiB behind it
+constexpr int PSMEM_BAR = PSMEM_PAIR + NPS * TILE_BYTES;
+constexpr int PSMEM_MISC = PSMEM_BAR + PB_COUNT * 8;
+constexpr int PSMEM_DYN = PSMEM_MISC + 16 + 1024;
+
+template <typename T, typename OT>
+__global__ void __launch_bounds__(NUM_THREADS, 1) prefill_pair_kernel(
+    const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+    const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar0 = smem_base + PSMEM_BAR;
+    auto bar = [bar0](int i) { return bar0 + 8u * i; };                    // this CTA's barrier
+    auto lbar = [bar0](int i) { return map_to_cta(bar0 + 8u * i, 0u); };   // the even CTA's barrier (cluster address)
+    volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem_gen + PSMEM_MISC);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem_gen + PSMEM_MISC + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta = cluster_ctarank();
+    const int pb = p.num_qblocks - 1 - (int)(blockIdx.x >> 1);            // heaviest pair first (num_qblocks counts pairs here)
+    const int head = blockIdx.y, b = blockIdx.z;
+    const int kvh = head / p.group;
+
+    const int q_len = p.q_len[b];
+    const int m0p = pb * (2 * QT * BM);
+    if (m0p >= q_len) return;                                              // the same decision in both CTAs of the pair
+    const int m0 = m0p + (int)cta * (QT * BM);
+    const int kv_len = p.kv_len[b];
+    const int q_start = p.q_start[b], kv_start = p.kv_start[b];
+    const int dnum = p.kv_first[b] - p.q_first[b];
+    const int delta = dnum >= 0 ? (dnum + p.stride_s - 1) / p.stride_s : -((-dnum) / p.stride_s);
+    // kv tiles a slot needs = what its later rows (the odd CTA's) need; the even CTA's rows see nothing in the extra tiles
+    int nslot[QT];
+#pragma unroll
+    for (int t = 0; t < QT; ++t) {
+        int cnt = 0;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int r0 = m0p + c * (QT * BM) + t * BM;
+            if (r0 < q_len) {
+                const int last_row = min(r0 + BM - 1, q_len - 1);
+                const int range = max(0, min(last_row - delta + 1, kv_len));
+                cnt = max(cnt, (range + BN - 1) / BN);
+            }
+        }
+        nslot[t] = cnt;
+    }
+    const int nmax = max(nslot[0], nslot[1]);
+    if (nmax == 0) return;                                                 // pair-uniform as well
+
+    if (threadIdx.x == 0) {
+        // after a reported timeout later CTAs drain: every wait gives up at once, but both CTAs of a pair still walk
+        // through the cluster barriers below together
+        *s_abort = (*reinterpret_cast<volatile int*>(&g_esp_status[0]) != 0) ? 1 : 0;
+        for (int i = 0; i < PB_COUNT; ++i) {
+            const uint32_t cnt = (i >= PB_PREADY && i < PB_PREADY + QT) ? 2 * kPReadyArrivals : (i == PB_VCLEAN ? 2 : 1);
+            mbar_init(bar(i), cnt);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 8 && lane == 0) {
+        prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
+    }
+    __syncthreads();
+    if (warp == 9) {
+        tmem_alloc_pair(smem_base + PSMEM_MISC, TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                 // the peer's barriers are initialised before anything is counted on them
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    if (warp >= 8) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+      if (warp == 8) {
+        // ------------------------------------------------------------------ TMA producer (one per CTA, own halves)
+        if (lane == 0 && !*s_abort) {       // when draining after a reported timeout nothing is loaded: the CTA leaves at once
+#pragma unroll
+            for (int t = 0; t < QT; ++t) {
+                if (nslot[t] > 0) {
+                    const uint32_t dst = smem_base + PSMEM_Q + t * TILE_BYTES;
+                    if (cta == 0) mbar_expect_tx(bar(PB_QFULL + t), 2 * TILE_BYTES);
+                    tma_load_3d_pair(dst, &tm_q, lbar(PB_QFULL + t), 0, head, q_start + m0 + t * BM);
+                    tma_load_3d_pair(dst + HALF_BYTES, &tm_q, lbar(PB_QFULL + t), 64, head, q_start + m0 + t * BM);
+                }
+            }
+            auto load_k_half = [&](uint32_t dst, int tile, uint32_t full_bar) {       // keys [64 cta, 64 cta + 64) of the tile
+                tma_load_3d_pair(dst, &tm_k, full_bar, 0, kvh, kv_start + tile * BN + 64 * (int)cta);
+                tma_load_3d_pair(dst + HALF_TILE / 2, &tm_k, full_bar, 64, kvh, kv_start + tile * BN + 64 * (int)cta);
+            };
+            if (cta == 0) mbar_expect_tx(bar(PB_K0FULL), 2 * HALF_TILE);
+            load_k_half(smem_base + PSMEM_K0, 0, lbar(PB_K0FULL));
+            for (int pr = 0; pr < nmax; ++pr) {
+                const int st = pr % NPS;
+                if (pr >= NPS && !bounded_wait(bar(PB_PEMPTY + st), ((pr / NPS) - 1) & 1, s_abort, 1, pr)) break;
+                const bool with_k = pr + 1 < nmax;
+                if (cta == 0) mbar_expect_tx(bar(PB_PFULL + st), with_k ? 4 * HALF_TILE : 2 * HALF_TILE);
+                const uint32_t vdst = smem_base + PSMEM_PAIR + st * TILE_BYTES;
+                tma_load_3d_pair(vdst, &tm_v, lbar(PB_PFULL + st), 64 * (int)cta, kvh, kv_start + pr * BN);   // dims [64 cta, +64)
+                if (with_k) load_k_half(vdst + HALF_TILE, pr + 1, lbar(PB_PFULL + st));
+            }
+        }
+      } else if (warp == 9) {
+        // ------------------------------------------------------------------ MMA issuer (even CTA only)
+        if (cta == 0 && lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc(Fmt<T>::kAB, 0, 2 * BM, BN);
+            constexpr uint32_t idesc_pv = make_idesc(Fmt<T>::kAB, 1, 2 * BM, HD);
+            auto issue_s = [&](int t, uint32_t kb) {          // kb: this CTA's K half, two 8 KiB panels of 64 rows
+                const uint32_t qa = smem_base + PSMEM_Q + t * TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k)
+                    umma_pair_ss(tmem_base + t * BN, desc_kmajor_sw128(qa + (k >> 2) * HALF_BYTES + (k & 3) * 32),
+                                 desc_kmajor_sw128(kb + (k >> 2) * (HALF_TILE / 2) + (k & 3) * 32), idesc_s, k > 0);
+            };
+            auto issue_pv = [&](int t, uint32_t vb, bool acc) {    // vb: this CTA's V half, one panel of 128 keys x 64 dims
+#pragma unroll
+                for (int k = 0; k < BN / 16; ++k)
+                    umma_pair_ts(tmem_base + QT * BN + t * HD, tmem_base + t * BN + k * 8,
+                                 desc_mnmajor_sw128(vb + k * 2048, HALF_TILE), idesc_pv, (acc || k > 0) ? 1u : 0u);
+            };
+            bool ok = bounded_wait(bar(PB_K0FULL), 0, s_abort, 3, 0);
+#pragma unroll
+            for (int t = 0; t < QT; ++t)
+                if (nslot[t] > 0) ok = ok && bounded_wait(bar(PB_QFULL + t), 0, s_abort, 2, t);
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int t = 0; t < QT; ++t)
+                    if (nslot[t] > 0) { issue_s(t, smem_base + PSMEM_K0); umma_pair_commit(bar(PB_SFULL + t)); }
+            }
+            for (int j = 0; j < nmax && ok; ++j) {
+                const int st = j % NPS;
+                const uint32_t vb = smem_base + PSMEM_PAIR + st * TILE_BYTES;
+                ok = bounded_wait(bar(PB_PFULL + st), (j / NPS) & 1, s_abort, 4, j);          // V_j and K_j+1, both CTAs' halves
+                if (!ok) break;
+                if ((j + 1) * BN > kv_len) {
+                    // the request's last, partly filled kv tile (at most one per pair): each CTA's sanitizer warp zeroes the
+                    // rows of its V half behind the last key (P = 0 does not cancel a NaN), then this thread goes on
+                    mbar_arrive(bar(PB_VREQ));
+                    mbar_arrive_cluster(map_to_cta(bar(PB_VREQ), 1u));
+                    ok = bounded_wait(bar(PB_VCLEAN), 0, s_abort, 5, j);
+                    if (!ok) break;
+                }
+#pragma unroll
+                for (int t = 0; t < QT; ++t) {
+                    if (j < nslot[t]) {
+                        ok = bounded_wait(bar(PB_PREADY + t), j & 1, s_abort, 6 + t, j);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_pv(t, vb, j > 0);
+                        if (j == nslot[t] - 1) umma_pair_commit(bar(PB_ODONE + t));
+                    }
+                    if (j + 1 < nslot[t]) {
+                        issue_s(t, vb + HALF_TILE);
+                        umma_pair_commit(bar(PB_SFULL + t));
+                    }
+                }
+                if (!ok) break;
+                umma_pair_commit(bar(PB_PEMPTY + st));
+            }
+        }
+        __syncwarp();
+      } else if (warp == 10) {
+        // ------------------------------------------------------------------ sanitizer of this CTA's V half (see the issuer)
+        const int tail_j = kv_len / BN;
+        if ((kv_len % BN) != 0 && tail_j < nmax) {
+            bool go = bounded_wait(bar(PB_VREQ), 0, s_abort, 13, tail_j);
+            go = __all_sync(0xffffffffu, go);
+            if (go) {
+                const int first_bad = kv_len - tail_j * BN;
+                uint8_t* vs = smem_gen + PSMEM_PAIR + (tail_j % NPS) * TILE_BYTES;
+                for (int i = first_bad * 8 + lane; i < BN * 8; i += 32)           // 8 x 16 B per 128 B row
+                    *reinterpret_cast<uint4*>(vs + i * 16) = make_uint4(0, 0, 0, 0);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(lbar(PB_VCLEAN));
+            }
+        }
+      }
+    } else {
+        // ------------------------------------------------------------------ softmax + epilogue (as in the single-CTA kernel)
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+        const int t = warp >> 2;                       // q tile of this warpgroup
+        const int nt = nslot[t];              // both CTAs walk the slot's kv tiles together
+        if (nt > 0) {
+            const int row_in_tile = (warp & 3) * 32 + lane;
+            const int row = m0 + t * BM + row_in_tile;     // local row index inside the request
+            const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;
+            const uint32_t tS = tmem_base + lane_base + t * BN;
+            const uint32_t tO = tmem_base + lane_base + QT * BN + t * HD;
+            const float scale = p.scale_log2;
+            float m_run = -INFINITY, l_run = 0.f;
+            bool ok = true;
+            for (int j = 0; j < nt; ++j) {
+                ok = bounded_wait(bar(PB_SFULL + t), j & 1, s_abort, 8 + t, j);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t sr[4][32];
+                tmem_ld32(tS, sr[0]);
+                tmem_ld32(tS + 32, sr[1]);
+                tmem_wait_ld();
+                tmem_ld32(tS + 64, sr[2]);          // second half streams in while the first is reduced
+                tmem_ld32(tS + 96, sr[3]);
+                const int n0 = j * BN;
+                const int r0 = m0 + t * BM;
+                const bool masked = (n0 + BN - 1 > r0 - delta) || (n0 + BN > kv_len);
+                const int limit = min(row - delta, kv_len - 1) - n0;     // columns <= limit are visible
+                // After the first tile the running maximum rarely grows by more than the lazy-rescale threshold, so the
+                // exponentials of an unmasked tile are taken against the running maximum straight away, without looking
+                // for the tile's own maximum (every instruction of this loop counts: the softmax warps' instruction
+                // stream, with the issuing thread's, is what bounds the kernel).  P is stored only once every row of
+                // the warp is known to have stayed within the threshold -- its row sum proves it; otherwise S (still
+                // intact in tensor memory) is read again and the tile is done the slow way: maximum first, O rescaled,
+                // then the exponentials.
+                float lsum = 0.f;
+                bool published = false;
+                if (!masked && j > 0) {
+                    const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+                    uint32_t pa[32], pb[32];
+                    const float s0 = chunk_exp<T, 0>(sr[0], scale, neg_m, pa);
+                    const float s1 = chunk_exp<T, 16>(sr[1], scale, neg_m, pa);
+                    tmem_wait_ld();
+                    const float s2 = chunk_exp<T, 0>(sr[2], scale, neg_m, pb);
+                    const float s3 = chunk_exp<T, 16>(sr[3], scale, neg_m, pb);
+                    lsum = (s0 + s1) + (s2 + s3);
+                    // no exponential can exceed the row's sum of them: a sum within 2^threshold proves that the tile's maximum
+                    // stayed within the threshold (a larger sum, an infinity or a NaN sends the tile down the exact path)
+                    const bool outgrown = !(lsum <= kSpecSumLimit) || (m_run == -INFINITY);
+                    if (!__any_sync(0xffffffffu, outgrown)) {
+                        tmem_st32(tS, pa);
+                        tmem_st32(tS + 32, pb);
+                        published = true;
+                    } else {
+                        tmem_ld32(tS, sr[0]);
+                        tmem_ld32(tS + 32, sr[1]);
+                        tmem_wait_ld();
+                        tmem_ld32(tS + 64, sr[2]);
+                        tmem_ld32(tS + 96, sr[3]);
+                    }
+                }
+                if (!published) {
+                    float mx = fmaxf(chunk_max(sr[0], 0, limit, masked), chunk_max(sr[1], 32, limit, masked));
+                    tmem_wait_ld();
+                    mx = fmax3(mx, chunk_max(sr[2], 64, limit, masked), chunk_max(sr[3], 96, limit, masked));
+                    const float m_new = fmaxf(m_run, mx * scale);
+                    // lazy rescale: keep the old reference maximum unless the row maximum grew by > 2^8
+                    const bool need = (m_new > m_run + kRescaleThreshold) || (m_run == -INFINITY && m_new > -INFINITY);
+                    float alpha = 1.f;
+                    if (need) {
+                        alpha = ex2(m_run - m_new);       // 0 when the row had no key before
+                        l_run *= alpha;
+                        m_run = m_new;
+                    }
+                    if (j > 0 && __any_sync(0xffffffffu, need)) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t orow[32];
+                            tmem_ld32(tO + c * 32, orow);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                            tmem_st32(tO + c * 32, orow);
+                        }
+                    }
+                    const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+                    {
+                        uint32_t pk[32];
+                        const float s0 = chunk_exp<T, 0>(sr[0], scale, neg_m, pk);
+                        const float s1 = chunk_exp<T, 16>(sr[1], scale, neg_m, pk);
+                        tmem_st32(tS, pk);                 // P aliases the first 64 columns of S
+                        lsum = s0 + s1;
+                    }
+                    {
+                        uint32_t pk[32];
+                        const float s2 = chunk_exp<T, 0>(sr[2], scale, neg_m, pk);
+                        const float s3 = chunk_exp<T, 16>(sr[3], scale, neg_m, pk);
+                        tmem_st32(tS + 32, pk);
+                        lsum += s2 + s3;
+                    }
+                }
+                l_run += lsum;
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(lbar(PB_PREADY + t));      // the issuing thread lives in the even CTA
+            }
+            if (ok) {
+                ok = bounded_wait(bar(PB_ODONE + t), 0, s_abort, 10 + t, nt);
+                ok = __all_sync(0xffffffffu, ok);
+            }
+            if (ok) {
+                tc_fence_after();
+                const bool live = (row < q_len) && (l_run > 0.f);
+                const int64_t grow = (int64_t)q_start + row;
+                float a_old = 0.f, a_new = 0.f, inv_l = 0.f;
+                if (live) {
+                    const int64_t si = grow * p.num_q_heads + head;
+                    const float m_old = p.m[si], l_old = p.l[si];
+                    const float m_new = fmaxf(m_run, m_old);
+                    a_old = l_old * ex2(m_old - m_new);       // 0 for a fresh (-inf, 0) state
+                    a_new = ex2(m_run - m_new);
+                    const float l_new = a_old + l_run * a_new;
+                    inv_l = 1.f / l_new;
+                    p.m[si] = m_new;
+                    p.l[si] = l_new;
+                }
+                OT* orow_g = reinterpret_cast<OT*>(p.o) + grow * p.o_stride_t + (int64_t)head * p.o_stride_h;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t acc[32];
+                    tmem_ld32(tO + c * 32, acc);
+                    tmem_wait_ld();
+                    if (live) {
+                        float x[32];
+                        if (a_old != 0.f) {
+                            load_row32<OT>(orow_g + c * 32, x);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                x[i] = (x[i] * a_old + __uint_as_float(acc[i]) * a_new) * inv_l;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(acc[i]) * (a_new * inv_l);
+                        }
+                        store_row32<OT>(orow_g + c * 32, x);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                 // neither CTA frees tensor memory or leaves while the peer's MMAs may still use it
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -530,14 +890,14 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-// [tokens, heads, 128] 16-bit tensor, box = 64 dims x 1 head x 128 tokens, 128-byte swizzle.
+// [tokens, heads, 128] 16-bit tensor, box = 64 dims x 1 head x `box_tokens` tokens, 128-byte swizzle.
 static int make_tile_map(CUtensorMap* tm, const void* base, int64_t tokens, int heads, int64_t stride_t,
-                         int64_t stride_h, int dtype) {
+                         int64_t stride_h, int dtype, int box_tokens = BN) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) { snprintf(last_cuda_error_buf(), 256, "cuTensorMapEncodeTiled entry point not found"); return ESP_ERR_CUDA; }
     cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)tokens};
     cuuint64_t strides[2] = {(cuuint64_t)stride_h * 2, (cuuint64_t)stride_t * 2};
-    cuuint32_t box[3] = {64, 1, (cuuint32_t)BN};
+    cuuint32_t box[3] = {64, 1, (cuuint32_t)box_tokens};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(tm, dtype == ESP_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                     3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -568,6 +928,33 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
     prefill_step_kernel<T, OT><<<grid, NUM_THREADS, SMEM_DYN, s>>>(tq, tk, tv, pp);
     ESP_LAUNCH_CHECK("prefill_step_kernel");
     return ESP_OK;
+}
+
+template <typename T, typename OT>
+static int launch_prefill_pair(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                               const PrefillParams& pp, dim3 grid, cudaStream_t s) {
+    ESP_CUDA_TRY(cudaFuncSetAttribute(prefill_pair_kernel<T, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, PSMEM_DYN));
+    cudaFuncAttributes fa;
+    ESP_CUDA_TRY(cudaFuncGetAttributes(&fa, prefill_pair_kernel<T, OT>));
+    if (fa.numRegs * NUM_THREADS < 256 * kRegsSoftmax + 128 * kRegsOther) {
+        snprintf(last_cuda_error_buf(), 256, "prefill pair kernel was built with %d registers per thread, too few for its setmaxnreg plan", fa.numRegs);
+        return ESP_ERR_UNSUPPORTED;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = PSMEM_DYN; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    ESP_CUDA_TRY(cudaLaunchKernelEx(&cfg, prefill_pair_kernel<T, OT>, tq, tk, tv, pp));
+    return ESP_OK;
+}
+
+// Requests longer than one 256-row block run on CTA pairs; ESP_PREFILL_PAIRS=0 in the environment keeps the single-CTA kernel.
+static bool use_pairs(int max_q_len) {
+    static int env = -1;
+    if (env < 0) { const char* e = getenv("ESP_PREFILL_PAIRS"); env = (e && e[0] == '0') ? 0 : 1; }
+    return env == 1 && max_q_len > QT * BM;
 }
 
 __global__ void state_init_kernel(float* m, float* l, int64_t n) {
@@ -614,8 +1001,9 @@ extern "C" int esp_prefill_step(const void* q, int64_t q_stride_t, int64_t q_str
         return ESP_ERR_ALIGNMENT;
     CUtensorMap tq, tk, tv;
     int rc;
+    const bool pairs = use_pairs(max_q_b_seq_len);
     if ((rc = make_tile_map(&tq, q, q_tokens, num_q_heads, q_stride_t, q_stride_h, dtype))) return rc;
-    if ((rc = make_tile_map(&tk, k, kv_tokens, num_kv_heads, kv_stride_t, kv_stride_h, dtype))) return rc;
+    if ((rc = make_tile_map(&tk, k, kv_tokens, num_kv_heads, kv_stride_t, kv_stride_h, dtype, pairs ? BN / 2 : BN))) return rc;
     if ((rc = make_tile_map(&tv, v, kv_tokens, num_kv_heads, kv_stride_t, kv_stride_h, dtype))) return rc;
     PrefillParams pp;
     pp.o = o; pp.m = m; pp.l = l; pp.o_stride_t = o_stride_t; pp.o_stride_h = o_stride_h;
@@ -626,6 +1014,15 @@ extern "C" int esp_prefill_step(const void* q, int64_t q_stride_t, int64_t q_str
     pp.scale_log2 = (sm_scale > 0.f ? sm_scale : 1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
     dim3 grid(pp.num_qblocks, num_q_heads, batch);
     cudaStream_t s = (cudaStream_t)stream;
+    if (pairs) {
+        pp.num_qblocks = (max_q_b_seq_len + 2 * QT * BM - 1) / (2 * QT * BM);       // pairs of 256-row blocks
+        grid.x = 2 * pp.num_qblocks;
+        if (dtype == ESP_DTYPE_F16)
+            return o_dtype == ESP_DTYPE_F32 ? launch_prefill_pair<__half, float>(tq, tk, tv, pp, grid, s)
+                                            : launch_prefill_pair<__half, __half>(tq, tk, tv, pp, grid, s);
+        return o_dtype == ESP_DTYPE_F32 ? launch_prefill_pair<__nv_bfloat16, float>(tq, tk, tv, pp, grid, s)
+                                        : launch_prefill_pair<__nv_bfloat16, __nv_bfloat16>(tq, tk, tv, pp, grid, s);
+    }
     if (dtype == ESP_DTYPE_F16)
         return o_dtype == ESP_DTYPE_F32 ? launch_prefill<__half, float>(tq, tk, tv, pp, grid, s)
                                         : launch_prefill<__half, __half>(tq, tk, tv, pp, grid, s);
