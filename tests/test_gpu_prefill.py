@@ -60,6 +60,41 @@ def test_single_step_varlen_matches_oracle(dtype, Hq, Hkv, o_fp32):
     _check(o, ro, ca.attention_lse(m, l), rlse)
 
 
+@pytest.mark.parametrize("q_len", [256, 512])          # 256 rows: single-CTA kernel; 512: CTA-pair kernel
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_scores_that_outgrow_the_running_maximum(q_len, dtype):
+    """After its first KV tile the kernel takes exponentials against the RUNNING maximum and keeps them only when the row
+    sum proves no score grew past the lazy-rescale threshold (2^8).  Keys here are built to leave that path in every way:
+    scores that jump far above the maximum mid-sequence, a jump confined to the second half of a 128-key tile, a jump
+    in a single row of a warp, many moderately larger scores (row sum over the limit although no score is), and
+    scores that fall far below.  All keys are visible to all rows (a block from an earlier instance of the ring)."""
+    ca = _ca()
+    Hq, Hkv, D, kv_len = 4, 2, 128, 1280
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(q_len, Hq, D, generator=g)
+    k = torch.randn(kv_len, Hkv, D, generator=g) * 0.3
+    v = torch.randn(kv_len, Hkv, D, generator=g)
+    q[:, :, 0] = 4.0; k[:, :, 0] = 0.0
+    k[128:256] *= 0.01                                    # tile 1: far below the maximum of tile 0
+    k[256:384, 0, 0] = 10.0                               # tile 2, kv head 0: every score about 2^4 above (sum, not max, over the limit)
+    k[448:512] *= 12.0                                    # tile 3, second half only: large scores of both signs
+    k[700, 1] = 40.0 * q[37, 2] / q[37, 2].norm()         # tile 5: one key that one row (and a few others) scores hugely
+    k[1024:1152] *= 30.0                                  # tile 8: everything jumps
+    k[1152:] *= 0.5
+    q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    for o_dtype in (dtype, torch.float32):
+        ro = torch.zeros(q_len, Hq, D, dtype=o_dtype)
+        rm = torch.full((q_len, Hq), float("-inf")); rl = torch.zeros(q_len, Hq)
+        O.ring_step(q, k, v, ro, rm, rl, [0], [q_len], [kv_len], [0], [kv_len], [0], 1)
+        o = torch.full((q_len, Hq, D), float("nan"), dtype=o_dtype, device=DEV)
+        m = torch.empty(q_len, Hq, device=DEV); l = torch.empty(q_len, Hq, device=DEV)
+        ca.init_attention_state(None, m, l)
+        ca.context_attention_fwd(q.to(DEV), k.to(DEV), v.to(DEV), o, _i32([0]), _i32([q_len]), _i32([kv_len]),
+                                 _i32([0]), _i32([kv_len]), _i32([0]), 1, q_len, m, l)
+        _status_ok()
+        _check(o, ro, ca.attention_lse(m, l), O.lse_from_state(rm, rl))
+
+
 @pytest.mark.parametrize("name", ["ring_ref_contig_p2.npz", "ring_ref_striped_p4.npz"])
 def test_ring_steps_match_reference_kernel_golden(golden_dir, name):
     """Step-by-step (o, lse) of every rank against what the reference's Triton kernel produced (fp16)."""
