@@ -35,8 +35,9 @@ const char* esp_strerror(int code);
 /* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
 const char* esp_last_cuda_error(void);
 /* ABI version of this header (bumped on incompatible change).  Version 2: the peer-memory entry points take `value_base`.
- * Version 3: the kernels that dereference slot ids take the pool's row count; the self-test kernels left the library. */
-#define ESP_ABI_VERSION 3
+ * Version 3: the kernels that dereference slot ids take the pool's row count; the self-test kernels left the library.
+ * Version 4: esp_prefill_step_strided added (nothing removed or changed). */
+#define ESP_ABI_VERSION 4
 int esp_abi_version(void);
 
 /* ------------------------------------------------------------------------------------------------
@@ -70,6 +71,24 @@ int esp_prefill_step(const void* q, int64_t q_stride_t, int64_t q_stride_h, int6
                      int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
                      int32_t logical_sp_peers_num, int32_t max_q_b_seq_len, int32_t dtype,
                      int32_t o_dtype, float sm_scale, void* stream);
+
+/* The same step with separate position strides for q rows and keys: key n of request b is visible to q row r iff
+ *   q_first[b] + r*q_pos_stride >= kv_first[b] + n*kv_pos_stride  and  n < kv_len[b]
+ * (q_pos_stride a positive multiple of kv_pos_stride; the firsts may be negative).  esp_prefill_step is this call with both
+ * strides equal to logical_sp_peers_num.  With q_pos_stride = P-1 and kv_pos_stride = 1 one call attends the local q rows of
+ * instance r of a striped ring of P to the KV rows of ALL other instances gathered into one buffer in position order
+ * (row n*(P-1) + i holds token n of the i-th other instance): q_first = r - 1, kv_first = 0 -- what the reference's ring
+ * loop does in P-1 steps (longserve_transformer_layer_infer.py:128-181). */
+int esp_prefill_step_strided(const void* q, int64_t q_stride_t, int64_t q_stride_h, int64_t q_tokens,
+                             const void* k, const void* v, int64_t kv_stride_t, int64_t kv_stride_h,
+                             int64_t kv_tokens,
+                             void* o, int64_t o_stride_t, int64_t o_stride_h, float* m, float* l,
+                             const int32_t* q_b_start_loc, const int32_t* q_b_seq_len,
+                             const int32_t* q_first_token_global_idx, const int32_t* kv_b_start_loc,
+                             const int32_t* kv_b_seq_len, const int32_t* kv_first_token_global_idx,
+                             int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                             int32_t q_pos_stride, int32_t kv_pos_stride, int32_t max_q_b_seq_len,
+                             int32_t dtype, int32_t o_dtype, float sm_scale, void* stream);
 
 /* Reset the running state before the first ring step: o = 0, m = -inf, l = 0
  * (longserve_transformer_layer_infer.py:123-126).  o may be NULL. */

@@ -18,12 +18,14 @@ ESP_DTYPE_F16, ESP_DTYPE_BF16, ESP_DTYPE_F32 = 0, 1, 2
 _i32, _i64, _f32, _vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
 
 # name -> argtypes, exactly as declared in include/esp_attention.h
-ESP_ABI_VERSION = 3      # what esp_abi_version() of a matching library returns (see include/esp_attention.h)
+ESP_ABI_VERSION = 4      # what esp_abi_version() of a matching library returns (see include/esp_attention.h)
 
 ATTN_SIGNATURES = {
     "esp_abi_version": [],
     "esp_prefill_step": [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _vp,
                          _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
+    "esp_prefill_step_strided": [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _vp,
+                                 _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
     "esp_prefill_state_init": [_vp, _i64, _vp, _vp, _i64, _vp],
     "esp_prefill_lse": [_vp, _vp, _vp, _i64, _vp],
     "esp_device_status": [C.POINTER(_i32), _i32],

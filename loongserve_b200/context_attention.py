@@ -12,7 +12,8 @@ from ._util import dtype_tag, need_cuda, need_i32, ptr, stream_ptr
 @torch.inference_mode()
 def context_attention_fwd(q, k, v, o, q_b_start_loc, q_b_seq_len, q_first_token_global_idx,
                           kv_b_start_loc, kv_b_seq_len, kv_first_token_global_idx,
-                          logical_sp_peers_num: int, max_q_b_seq_len: int, m, l, sm_scale: float = 0.0):
+                          logical_sp_peers_num: int, max_q_b_seq_len: int, m, l, sm_scale: float = 0.0,
+                          kv_pos_stride: int = None):
     """Attention between the local q and one local/remote KV block, merged into (o, m, l) in place.
 
     q, o: [num_q_tokens, num_q_heads, head_dim]; k, v: [num_kv_tokens, num_kv_heads, head_dim] (views
@@ -20,6 +21,9 @@ def context_attention_fwd(q, k, v, o, q_b_start_loc, q_b_seq_len, q_first_token_
     m, l: fp32 [num_q_tokens, num_q_heads]; the six metadata vectors are int32 [batch].
     ``o`` may be q's dtype (reference behaviour) or float32.  Before the first step of a ring pass
     set m = -inf and l = 0 (o need not be cleared).
+
+    ``kv_pos_stride`` (default: ``logical_sp_peers_num``) is the position stride of consecutive keys when it differs from
+    that of consecutive q rows (``logical_sp_peers_num``): 1 for a buffer that holds the other instances' rows in position order.
     """
     need_cuda(q, k, v, o, m, l, q_b_start_loc)
     need_i32(q_b_start_loc, q_b_seq_len, q_first_token_global_idx, kv_b_start_loc, kv_b_seq_len,
@@ -33,15 +37,16 @@ def context_attention_fwd(q, k, v, o, q_b_start_loc, q_b_seq_len, q_first_token_
     assert m.dtype == torch.float32 and l.dtype == torch.float32 and m.is_contiguous() and l.is_contiguous()
     assert m.shape == (q.shape[0], q.shape[1]) and l.shape == m.shape
     batch = q_b_seq_len.shape[0]
-    rc = _lib.attn().esp_prefill_step(
+    rc = _lib.attn().esp_prefill_step_strided(
         ptr(q), q.stride(0), q.stride(1), q.shape[0],
         ptr(k), ptr(v), k.stride(0), k.stride(1), k.shape[0],
         ptr(o), o.stride(0), o.stride(1), ptr(m), ptr(l),
         ptr(q_b_start_loc), ptr(q_b_seq_len), ptr(q_first_token_global_idx),
         ptr(kv_b_start_loc), ptr(kv_b_seq_len), ptr(kv_first_token_global_idx),
-        batch, q.shape[1], k.shape[1], Lq, int(logical_sp_peers_num), int(max_q_b_seq_len),
+        batch, q.shape[1], k.shape[1], Lq, int(logical_sp_peers_num),
+        int(logical_sp_peers_num if kv_pos_stride is None else kv_pos_stride), int(max_q_b_seq_len),
         dtype_tag(q), dtype_tag(o), float(sm_scale), stream_ptr())
-    _lib.check(rc, "esp_prefill_step")
+    _lib.check(rc, "esp_prefill_step_strided")
 
 
 @torch.inference_mode()

@@ -73,7 +73,7 @@ struct PrefillParams {
     int64_t o_stride_t, o_stride_h;
     const int32_t* q_start; const int32_t* q_len; const int32_t* q_first;
     const int32_t* kv_start; const int32_t* kv_len; const int32_t* kv_first;
-    int num_q_heads, group, stride_s, num_qblocks;
+    int num_q_heads, group, q_pos_stride, kv_pos_stride, num_qblocks;   // position strides of consecutive q rows / keys
     float scale_log2;
 };
 
@@ -207,9 +207,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
     if (m0 >= q_len) return;
     const int kv_len = p.kv_len[b];
     const int q_start = p.q_start[b], kv_start = p.kv_start[b];
-    // key n visible to local row r  <=>  n <= r - delta  and  n < kv_len
-    const int dnum = p.kv_first[b] - p.q_first[b];
-    const int delta = dnum >= 0 ? (dnum + p.stride_s - 1) / p.stride_s : -((-dnum) / p.stride_s);
+    // key n visible to local row r  <=>  n <= vis_a * r + vis_c  and  n < kv_len
+    const int dnum = p.q_first[b] - p.kv_first[b];
+    const int vis_a = p.q_pos_stride / p.kv_pos_stride;      // keys that become visible per q row (1 within a ring step)
+    const int vis_c = dnum >= 0 ? dnum / p.kv_pos_stride : -((-dnum + p.kv_pos_stride - 1) / p.kv_pos_stride);   // floor
     int n_tiles[QT];
 #pragma unroll
     for (int t = 0; t < QT; ++t) {
@@ -217,7 +218,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
         int cnt = 0;
         if (r0 < q_len) {
             const int last_row = min(r0 + BM - 1, q_len - 1);
-            const int range = max(0, min(last_row - delta + 1, kv_len));
+            const int range = max(0, min(vis_a * last_row + vis_c + 1, kv_len));
             cnt = (range + BN - 1) / BN;
         }
         n_tiles[t] = cnt;
@@ -378,8 +379,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                 tmem_ld32(tS + 96, sr[3]);
                 const int n0 = j * BN;
                 const int r0 = m0 + t * BM;
-                const bool masked = (n0 + BN - 1 > r0 - delta) || (n0 + BN > kv_len);
-                const int limit = min(row - delta, kv_len - 1) - n0;     // columns <= limit are visible
+                const bool masked = (n0 + BN - 1 > vis_a * r0 + vis_c) || (n0 + BN > kv_len);
+                const int limit = min(vis_a * row + vis_c, kv_len - 1) - n0;     // columns <= limit are visible
                 // After the first tile the running maximum rarely grows by more than the lazy-rescale threshold, so the
                 // exponentials of an unmasked tile are taken against the running maximum straight away, without looking
                 // for the tile's own maximum (every instruction of this loop counts: the softmax warps' instruction
@@ -557,8 +558,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_pair_kernel(
     const int m0 = m0p + (int)cta * (QT * BM);
     const int kv_len = p.kv_len[b];
     const int q_start = p.q_start[b], kv_start = p.kv_start[b];
-    const int dnum = p.kv_first[b] - p.q_first[b];
-    const int delta = dnum >= 0 ? (dnum + p.stride_s - 1) / p.stride_s : -((-dnum) / p.stride_s);
+    const int dnum = p.q_first[b] - p.kv_first[b];
+    const int vis_a = p.q_pos_stride / p.kv_pos_stride;      // keys that become visible per q row (1 within a ring step)
+    const int vis_c = dnum >= 0 ? dnum / p.kv_pos_stride : -((-dnum + p.kv_pos_stride - 1) / p.kv_pos_stride);   // floor
     // kv tiles a slot needs = what its later rows (the odd CTA's) need; the even CTA's rows see nothing in the extra tiles
     int nslot[QT];
 #pragma unroll
@@ -569,7 +571,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_pair_kernel(
             const int r0 = m0p + c * (QT * BM) + t * BM;
             if (r0 < q_len) {
                 const int last_row = min(r0 + BM - 1, q_len - 1);
-                const int range = max(0, min(last_row - delta + 1, kv_len));
+                const int range = max(0, min(vis_a * last_row + vis_c + 1, kv_len));
                 cnt = max(cnt, (range + BN - 1) / BN);
             }
         }
@@ -736,8 +738,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_pair_kernel(
                 tmem_ld32(tS + 96, sr[3]);
                 const int n0 = j * BN;
                 const int r0 = m0 + t * BM;
-                const bool masked = (n0 + BN - 1 > r0 - delta) || (n0 + BN > kv_len);
-                const int limit = min(row - delta, kv_len - 1) - n0;     // columns <= limit are visible
+                const bool masked = (n0 + BN - 1 > vis_a * r0 + vis_c) || (n0 + BN > kv_len);
+                const int limit = min(vis_a * row + vis_c, kv_len - 1) - n0;     // columns <= limit are visible
                 // After the first tile the running maximum rarely grows by more than the lazy-rescale threshold, so the
                 // exponentials of an unmasked tile are taken against the running maximum straight away, without looking
                 // for the tile's own maximum (every instruction of this loop counts: the softmax warps' instruction
@@ -986,11 +988,27 @@ extern "C" int esp_prefill_step(const void* q, int64_t q_stride_t, int64_t q_str
                                 int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
                                 int32_t logical_sp_peers_num, int32_t max_q_b_seq_len, int32_t dtype,
                                 int32_t o_dtype, float sm_scale, void* stream) {
+    return esp_prefill_step_strided(q, q_stride_t, q_stride_h, q_tokens, k, v, kv_stride_t, kv_stride_h, kv_tokens, o, o_stride_t,
+                                    o_stride_h, m, l, q_b_start_loc, q_b_seq_len, q_first_token_global_idx, kv_b_start_loc,
+                                    kv_b_seq_len, kv_first_token_global_idx, batch, num_q_heads, num_kv_heads, head_dim,
+                                    logical_sp_peers_num, logical_sp_peers_num, max_q_b_seq_len, dtype, o_dtype, sm_scale, stream);
+}
+
+extern "C" int esp_prefill_step_strided(const void* q, int64_t q_stride_t, int64_t q_stride_h, int64_t q_tokens,
+                                        const void* k, const void* v, int64_t kv_stride_t, int64_t kv_stride_h,
+                                        int64_t kv_tokens, void* o, int64_t o_stride_t, int64_t o_stride_h,
+                                        float* m, float* l, const int32_t* q_b_start_loc,
+                                        const int32_t* q_b_seq_len, const int32_t* q_first_token_global_idx,
+                                        const int32_t* kv_b_start_loc, const int32_t* kv_b_seq_len,
+                                        const int32_t* kv_first_token_global_idx, int32_t batch,
+                                        int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                        int32_t q_pos_stride, int32_t kv_pos_stride, int32_t max_q_b_seq_len,
+                                        int32_t dtype, int32_t o_dtype, float sm_scale, void* stream) {
     if (batch == 0 || max_q_b_seq_len <= 0 || q_tokens == 0 || kv_tokens == 0) return ESP_OK;
     if (!q || !k || !v || !o || !m || !l || !q_b_start_loc || !q_b_seq_len || !q_first_token_global_idx ||
         !kv_b_start_loc || !kv_b_seq_len || !kv_first_token_global_idx || batch < 0 || num_q_heads <= 0 ||
-        num_kv_heads <= 0 || num_q_heads % num_kv_heads || logical_sp_peers_num <= 0 || q_tokens < 0 ||
-        kv_tokens < 0)
+        num_kv_heads <= 0 || num_q_heads % num_kv_heads || q_pos_stride <= 0 || kv_pos_stride <= 0 ||
+        q_pos_stride % kv_pos_stride || q_tokens < 0 || kv_tokens < 0)
         return ESP_ERR_BAD_ARG;
     if (dtype != ESP_DTYPE_F16 && dtype != ESP_DTYPE_BF16) return ESP_ERR_BAD_ARG;
     if (o_dtype != dtype && o_dtype != ESP_DTYPE_F32) return ESP_ERR_BAD_ARG;
@@ -1009,7 +1027,8 @@ extern "C" int esp_prefill_step(const void* q, int64_t q_stride_t, int64_t q_str
     pp.o = o; pp.m = m; pp.l = l; pp.o_stride_t = o_stride_t; pp.o_stride_h = o_stride_h;
     pp.q_start = q_b_start_loc; pp.q_len = q_b_seq_len; pp.q_first = q_first_token_global_idx;
     pp.kv_start = kv_b_start_loc; pp.kv_len = kv_b_seq_len; pp.kv_first = kv_first_token_global_idx;
-    pp.num_q_heads = num_q_heads; pp.group = num_q_heads / num_kv_heads; pp.stride_s = logical_sp_peers_num;
+    pp.num_q_heads = num_q_heads; pp.group = num_q_heads / num_kv_heads;
+    pp.q_pos_stride = q_pos_stride; pp.kv_pos_stride = kv_pos_stride;
     pp.num_qblocks = (max_q_b_seq_len + QT * BM - 1) / (QT * BM);
     pp.scale_log2 = (sm_scale > 0.f ? sm_scale : 1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
     dim3 grid(pp.num_qblocks, num_q_heads, batch);

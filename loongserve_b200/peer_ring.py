@@ -55,6 +55,12 @@ class _CudaBackend:
     def copy(self, stream, dst_addr: int, src_addr: int, nbytes: int):
         _lib.check(self.lib.esp_memcpy_async(dst_addr, src_addr, nbytes, stream.cuda_stream), "esp_memcpy_async")
 
+    def copy2d(self, stream, dst_addr: int, dpitch: int, src_addr: int, spitch: int, width: int, rows: int):
+        if dpitch == width and spitch == width:
+            self.copy(stream, dst_addr, src_addr, width * rows)
+        else:
+            _lib.check(self.lib.esp_memcpy_2d(dst_addr, dpitch, src_addr, spitch, width, rows, 2, stream.cuda_stream), "esp_memcpy_2d")
+
     def record(self, stream):
         ev = torch.cuda.Event()
         ev.record(stream)
@@ -194,3 +200,118 @@ class CopyEngineRing:
         _lib.check(self._lib.esp_decode_device_status(buf, 0), "esp_decode_device_status")
         if buf[0] != 0:
             raise RuntimeError(f"ring exchange: device status {tuple(buf)} (code, block, wait id, awaited value)")
+
+
+WAIT_GATHER_CREDIT, WAIT_GATHER_ARRIVAL = 18, 19
+
+
+class CopyEngineGather:
+    """The other way to feed a striped ring pass on parts with memory to spare: instead of passing blocks round the ring
+    while P launches attend to them one by one, every instance copies its block into EVERY other instance's gather buffer
+    (one strided copy-engine transfer per request and peer, all peers at once over NVSwitch) while the attention over the
+    local block runs, and ONE more launch attends to everything gathered (``ring.gathered_context_attention``).  Rows are
+    interleaved in position order -- token n of the i-th other instance lands in row n*(P-1)+i of its request -- so that the
+    gathered buffer reads like one block whose keys advance by one position per row.
+
+    Flags as in ``CopyEngineRing``: ``arrived[s]`` in the receiver's region counts the passes whose block sender s has
+    delivered, ``credit[r]`` in the sender's region the passes for which receiver r's buffer is free again.  Every wait is
+    bounded; ``check()`` reports an expired one."""
+
+    def __init__(self, rank: int, world: int, gathered_bytes: int, all_gather_bytes: Optional[Callable[[bytes], List[bytes]]],
+                 device="cuda", backend=None, peer_bases: Optional[List[int]] = None, raw_buffer=None):
+        assert 0 <= rank < world <= 64
+        self.rank, self.world = rank, world
+        self.gathered_bytes = (int(gathered_bytes) + 255) // 256 * 256
+        self.off_flags = self.gathered_bytes
+        self.total = self.off_flags + 256 * 2
+        self.device = torch.device(device)
+        self.passes = 0
+        self._events = []
+        self._began = False
+        if backend is not None:
+            self.backend, self.peer_base, self.base = backend, list(peer_bases), peer_bases[rank]
+            self._lib, self._raw = None, raw_buffer
+            self.streams = {p: f"copy{p}" for p in range(world) if p != rank}
+            return
+        self._lib = _lib.attn()
+        self.backend = _CudaBackend(self.device)
+        base = C.c_void_p()
+        handle = (C.c_uint8 * 64)()
+        _lib.check(self._lib.esp_peer_buffer_create(self.total, C.byref(base), handle), "esp_peer_buffer_create")
+        self.base = base.value
+        handles = all_gather_bytes(bytes(handle))
+        self.peer_base = [None] * world
+        for r in range(world):
+            if r == rank:
+                self.peer_base[r] = self.base
+            else:
+                p = C.c_void_p()
+                _lib.check(self._lib.esp_peer_buffer_open((C.c_uint8 * 64)(*handles[r]), C.byref(p)), "esp_peer_buffer_open")
+                self.peer_base[r] = p.value
+        self.streams = {p: torch.cuda.Stream(device=self.device, priority=-1) for p in range(world) if p != rank}
+        self._raw = torch.as_tensor(_RawDeviceMemory(self.base, self.gathered_bytes), device=self.device)
+
+    def close(self):
+        if self._lib is None or self.base is None:
+            return
+        torch.cuda.synchronize(self.device)
+        self._raw = None
+        for r, p in enumerate(self.peer_base):
+            if p is not None and r != self.rank:
+                self._lib.esp_peer_buffer_close(p)
+        self._lib.esp_peer_buffer_destroy(self.base)
+        self.base = None
+
+    def gathered(self, rows: int, like: torch.Tensor) -> torch.Tensor:
+        """The gather buffer viewed as ``[rows, *like.shape[1:]]`` of ``like``'s dtype."""
+        row_bytes = like[0].numel() * like.element_size()
+        assert rows * row_bytes <= self.gathered_bytes, "gather buffer smaller than the pass needs"
+        return self._raw[:rows * row_bytes].view(like.dtype).view(rows, *like.shape[1:])
+
+    def _arrived_flag(self, owner: int, sender: int) -> int:
+        return self.peer_base[owner] + self.off_flags + 4 * sender
+
+    def _credit_flag(self, owner: int, receiver: int) -> int:
+        return self.peer_base[owner] + self.off_flags + 256 + 4 * receiver
+
+    def begin_pass(self):
+        """This instance's gather buffer is free (stream order: the launch that read it last is queued before this call):
+        tell every sender."""
+        assert not self._began, "the previous pass was not finished"
+        be, S = self.backend, self.backend.compute_stream()
+        self.passes += 1
+        self._began, self._events = True, []
+        for p in self.streams:
+            be.signal(S, self._credit_flag(p, self.rank), self.passes)
+
+    def push(self, peer: int, copies):
+        """Deliver this instance's block to ``peer``: ``copies`` is a list of ``(dst_offset_bytes, dst_pitch, src_address,
+        src_pitch, width_bytes, rows)`` strided copies into the peer's gather buffer.  The local block must be complete on
+        the compute stream when this is called."""
+        be, Cs = self.backend, self.streams[peer]
+        be.wait(Cs, be.record(be.compute_stream()))
+        be.flag_wait(Cs, self._credit_flag(self.rank, peer), self.passes, WAIT_GATHER_CREDIT)
+        for dst_off, dpitch, src, spitch, width, rows in copies:
+            assert dst_off + (rows - 1) * dpitch + width <= self.gathered_bytes if rows > 0 else True
+            be.copy2d(Cs, self.peer_base[peer] + dst_off, dpitch, src, spitch, width, rows)
+        be.signal(Cs, self._arrived_flag(peer, self.rank), self.passes)
+        self._events.append(be.record(Cs))
+
+    def wait_all(self):
+        """The compute stream waits until every other instance's block of this pass has arrived."""
+        be, S = self.backend, self.backend.compute_stream()
+        for p in self.streams:
+            be.flag_wait(S, self._arrived_flag(self.rank, p), self.passes, WAIT_GATHER_ARRIVAL)
+
+    def end_pass(self):
+        """Later work on the compute stream sees this instance's own copies finished (the local block may be overwritten)."""
+        be, S = self.backend, self.backend.compute_stream()
+        for ev in self._events:
+            be.wait(S, ev)
+        self._began = False
+
+    def check(self):
+        buf = (C.c_int32 * 4)()
+        _lib.check(self._lib.esp_decode_device_status(buf, 0), "esp_decode_device_status")
+        if buf[0] != 0:
+            raise RuntimeError(f"gather exchange: device status {tuple(buf)} (code, block, wait id, awaited value)")

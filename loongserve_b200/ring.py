@@ -144,6 +144,71 @@ def ring_context_attention(q, local_kv, o, m, l, *, rank: int, peers: Sequence[i
 
 
 @dataclass
+class GatherPlan:
+    """Layout of one instance's gather buffer for a striped pass over ``P`` instances (``peer_ring.CopyEngineGather``):
+    request b owns ``seq_len[b]`` rows from ``start_loc[b]``, holding the other instances' tokens of that request in
+    position order (token n of the i-th other instance in row n*(P-1)+i).  Seen from there the local q row r of instance
+    ``rank`` sits at position r*(P-1) + rank - 1 (``q_first``), keys at 0, 1, 2, ..."""
+    meta: BlockMeta                   # start_loc / seq_len of the gathered rows, first_idx = 0
+    q_first: torch.Tensor             # int32 [batch], rank - 1
+    rows: int
+    start_rows: List[int]             # start_loc on the host
+
+    @staticmethod
+    def build(lens: Sequence[int], P: int, rank: int, device):
+        local_len, _, _ = shard_lengths(lens, P, True)
+        others = [int(L) - local_len[rank][b] for b, L in enumerate(lens)]
+        meta = BlockMeta.from_lengths(others, [0] * len(lens), device)
+        starts, acc = [], 0
+        for n in others:
+            starts.append(acc); acc += n
+        return GatherPlan(meta, torch.full((len(lens),), rank - 1, dtype=torch.int32).to(device), acc, starts)
+
+
+def gathered_context_attention(q, local_kv, o, m, l, *, rank: int, lens: Sequence[int], P: int, metas: Sequence[BlockMeta],
+                               plans: Sequence[GatherPlan], max_len_in_batch: int, num_kv_heads: int,
+                               attention_fn: Callable, init_fn: Callable, gather):
+    """One layer's prefill pass on instance ``rank`` of a STRIPED ring of ``P`` in two launches instead of P: every
+    instance sends its block to all others with copy-engine transfers while it attends to its own block, then attends to
+    everything it was sent in one call.  Same result as ``ring_context_attention`` up to the order in which the partial
+    softmaxes are merged (longserve_transformer_layer_infer.py:128-181 does it block by block).  ``plans[r]`` is instance
+    r's ``GatherPlan`` (a pure function of the request lengths, so every instance can compute where its rows go in every
+    other instance's buffer).  Costs (P-1)/P of the whole KV of the batch in memory per instance; for batches where that is
+    too much, or scale-down bookkeeping is wanted (``keep``), use the ring."""
+    Hkv = num_kv_heads
+    init_fn(o, m, l)
+    me = metas[rank]
+    if P == 1:
+        attention_fn(q, local_kv[:, :Hkv, :], local_kv[:, Hkv:, :], o, me.start_loc, me.seq_len, me.first_idx,
+                     me.start_loc, me.seq_len, me.first_idx, 1, max_len_in_batch, m, l)
+        return o
+    row_bytes = local_kv[0].numel() * local_kv.element_size()
+    local_len, _, _ = shard_lengths(lens, P, True)
+    my_starts, acc = [], 0
+    for n in local_len[rank]:
+        my_starts.append(acc); acc += n
+    gather.begin_pass()
+    for step in range(1, P):
+        peer = (rank + step) % P
+        i = rank if rank < peer else rank - 1           # this instance's place among the peer's other instances
+        copies = [((plans[peer].start_rows[b] + i) * row_bytes, (P - 1) * row_bytes,
+                   local_kv.data_ptr() + my_starts[b] * row_bytes, row_bytes, row_bytes, n)
+                  for b, n in enumerate(local_len[rank]) if n > 0]
+        gather.push(peer, copies)
+    attention_fn(q, local_kv[:, :Hkv, :], local_kv[:, Hkv:, :], o, me.start_loc, me.seq_len, me.first_idx,
+                 me.start_loc, me.seq_len, me.first_idx, P, max_len_in_batch, m, l)
+    gather.wait_all()
+    plan = plans[rank]
+    if plan.rows > 0:
+        g = gather.gathered(plan.rows, local_kv)
+        attention_fn(q, g[:, :Hkv, :], g[:, Hkv:, :], o, me.start_loc, me.seq_len, plan.q_first,
+                     plan.meta.start_loc, plan.meta.seq_len, plan.meta.first_idx, P - 1, max_len_in_batch, m, l,
+                     kv_pos_stride=1)
+    gather.end_pass()
+    return o
+
+
+@dataclass
 class MasterPlan:
     """What a master instance needs for one multi-master decode step
     (longserve_model.py:505-533, longserve_transformer_layer_infer.py:268-281,312-367)."""

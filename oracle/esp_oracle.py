@@ -98,7 +98,7 @@ def full_causal_attention(q, k, v, lens, sm_scale=None):
 def ring_step(q, k, v, o, m, l,
               q_b_start_loc, q_b_seq_len, q_first_token_global_idx,
               kv_b_start_loc, kv_b_seq_len, kv_first_token_global_idx,
-              logical_sp_peers_num: int, sm_scale=None, round_acc_to=None):
+              logical_sp_peers_num: int, sm_scale=None, round_acc_to=None, kv_pos_stride=None):
     """One ring step: attention of the local q rows against one (local or remote) KV block, merged
     in place into the running state.  Semantics of ``context_attention_fwd``
     (ring_context_flashattention_nopad.py:191-284):
@@ -113,6 +113,11 @@ def ring_step(q, k, v, o, m, l,
     ``o`` may be any float dtype (it is read and written in that dtype, like the reference does with
     the q dtype); m and l are fp32.  ``round_acc_to`` optionally rounds the step's unnormalised
     accumulator to a dtype before the merge, as the reference does with fp16 (:183).
+
+    ``kv_pos_stride`` (not in the reference, whose keys and q rows always advance by the same stride): position stride of
+    consecutive keys when it differs from that of q rows; the visibility rule becomes
+    ``q_first[b] + r*s >= kv_first[b] + n*kv_pos_stride``.  Used to check attention over a buffer that holds several
+    instances' blocks interleaved in position order.
     """
     Tq, Hq, D = q.shape
     Hkv = k.shape[1]
@@ -129,7 +134,7 @@ def ring_step(q, k, v, o, m, l,
         kk = k[ks:ks + kl].float().repeat_interleave(g, dim=1).permute(1, 0, 2)   # [Hq, kl, D]
         vv = v[ks:ks + kl].float().repeat_interleave(g, dim=1).permute(1, 0, 2)
         rows = (qf + torch.arange(ql, dtype=torch.int64) * s_).view(1, -1, 1)
-        cols = (kf + torch.arange(kl, dtype=torch.int64) * s_).view(1, 1, -1)
+        cols = (kf + torch.arange(kl, dtype=torch.int64) * (s_ if kv_pos_stride is None else int(kv_pos_stride))).view(1, 1, -1)
         blk = 1024
         for r0 in range(0, ql, blk):
             r1 = min(ql, r0 + blk)

@@ -162,6 +162,58 @@ def test_ring_on_one_gpu_equals_full_attention(P, striped):
     _check(o, ro, lse, rlse)
 
 
+
+@pytest.mark.parametrize("P,long", [(2, True), (3, True), (4, True), (8, True), (4, False), (8, False)])
+def test_gathered_blocks_on_one_gpu_equal_full_attention(P, long):
+    """The two-launch form of a striped pass: every instance attends to its own block, then in ONE call to the rows of all
+    other instances interleaved in position order (keys advance one position per row, q rows P-1: the strided entry
+    point).  Request lengths include ones that no instance count divides, a request shorter than the ring, and one long
+    enough for the CTA-pair kernel (without it the single-CTA kernel runs)."""
+    from loongserve_b200 import ring as R
+    ca = _ca()
+    lens = [700, 129, 5, 2300, 1] if long else [700, 129, 5, 1]
+    Hq, Hkv, D = 4, 2, 128
+    T = sum(lens)
+    g = torch.Generator().manual_seed(21)
+    q = torch.randn(T, Hq, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+    ro, rlse = O.full_causal_attention(q, k, v, lens)
+    local_len, first, stride = O.shard_request_lengths(lens, P, True)
+    qs, ks, vs = (O.shard_tokens(x, lens, P, True) for x in (q, k, v))
+    outs, lses = [], []
+    for r in range(P):
+        plan = R.GatherPlan.build(lens, P, r, DEV)
+        # what the copy engines of the other instances would have written into this instance's gather buffer
+        gk = torch.full((plan.rows + 3, 2 * Hkv, D), float("nan"), dtype=torch.bfloat16)
+        for s in range(P):
+            if s == r:
+                continue
+            i = s if s < r else s - 1
+            src0 = 0
+            for b, n in enumerate(local_len[s]):
+                rows = plan.start_rows[b] + torch.arange(n) * (P - 1) + i
+                gk[rows, :Hkv] = ks[s][src0:src0 + n]; gk[rows, Hkv:] = vs[s][src0:src0 + n]
+                src0 += n
+        assert not torch.isnan(gk[:plan.rows].float()).any()          # the layout is dense
+        gk = gk.to(DEV)
+        Tq = qs[r].shape[0]
+        o = torch.empty(Tq, Hq, D, dtype=torch.bfloat16, device=DEV)
+        m = torch.empty(Tq, Hq, device=DEV); l = torch.empty(Tq, Hq, device=DEV)
+        ca.init_attention_state(o, m, l)
+        q_len = _i32(local_len[r]); q_start = torch.cumsum(q_len, 0, dtype=torch.int32) - q_len
+        blk = torch.cat([ks[r], vs[r]], dim=1).to(DEV)
+        mx = max(max(local_len[r]), 1)
+        ca.context_attention_fwd(qs[r].to(DEV), blk[:, :Hkv], blk[:, Hkv:], o, q_start, q_len, _i32(first[r]),
+                                 q_start, q_len, _i32(first[r]), stride, mx, m, l)
+        ca.context_attention_fwd(qs[r].to(DEV), gk[:, :Hkv], gk[:, Hkv:], o, q_start, q_len, plan.q_first,
+                                 plan.meta.start_loc, plan.meta.seq_len, plan.meta.first_idx, P - 1, mx, m, l, kv_pos_stride=1)
+        outs.append(o.cpu()); lses.append(ca.attention_lse(m, l).cpu())
+    _status_ok()
+    o = O.unshard_tokens(outs, lens, P, True); lse = O.unshard_tokens(lses, lens, P, True)
+    _check(o, ro, lse, rlse)
+
+
 def test_unsupported_head_dim_is_rejected():
     ca = _ca()
     q = torch.zeros(8, 2, 64, dtype=torch.float16, device=DEV)
