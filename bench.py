@@ -752,8 +752,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=T_TOTAL)
     ap.add_argument("--layout", default="striped", choices=["striped", "contiguous"])
-    ap.add_argument("--exchange", default="copy_engine", choices=["copy_engine", "nccl"],
-                    help="ring exchange at N > 1: copy-engine transfers into peer memory, or ncclSend/ncclRecv")
+    ap.add_argument("--exchange", default="gather", choices=["gather", "copy_engine", "nccl"],
+                    help="KV exchange at N > 1: every block copied to every instance by copy engines, two attention launches per "
+                         "pass (striped layout only); block-by-block ring with copy-engine transfers; or with ncclSend/ncclRecv")
     ap.add_argument("--no-overlap", action="store_true", help="NCCL exchange only: queue it behind the attention kernel")
     ap.add_argument("--skip-extras", action="store_true", help="skip e2e / decode / cpu baseline (profiling runs)")
     ap.add_argument("--decode-only", action="store_true", help="run only the decode part (profiling runs)")
@@ -823,11 +824,17 @@ def main():
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     q = torch.randn(Tl, H, D, generator=g, device=dev, dtype=torch.bfloat16)
     kv_local = torch.randn(max_tok, 2 * H, D, generator=g, device=dev, dtype=torch.bfloat16)
-    exchange = None
+    exchange = gather = plans = None
+    if P > 1 and args.exchange == "gather" and not striped:
+        args.exchange = "copy_engine"            # the gathered form relies on the striped placement
     if P > 1 and args.exchange == "copy_engine":
         from loongserve_b200.peer_ring import CopyEngineRing
         exchange = CopyEngineRing(rank, P, kv_local.numel() * 2, _gather_fn(dist, world), device=dev)
-    recv = [torch.empty_like(kv_local) for _ in range(2 if (P > 1 and exchange is None) else 0)]
+    if P > 1 and args.exchange == "gather":
+        from loongserve_b200.peer_ring import CopyEngineGather
+        plans = [ringmod.GatherPlan.build([T], P, r, dev) for r in range(P)]
+        gather = CopyEngineGather(rank, P, max(p_.rows for p_ in plans) * 2 * H * D * 2, _gather_fn(dist, world), device=dev)
+    recv = [torch.empty_like(kv_local) for _ in range(2 if (P > 1 and exchange is None and gather is None) else 0)]
     o = torch.empty_like(q)
     m = torch.empty(Tl, H, device=dev); l = torch.empty(Tl, H, device=dev)
 
@@ -840,6 +847,10 @@ def main():
             ca.context_attention_fwd(q, kv_local[:, :H], kv_local[:, H:], o, metas[0].start_loc, metas[0].seq_len,
                                      metas[0].first_idx, metas[0].start_loc, metas[0].seq_len, metas[0].first_idx,
                                      1, Tl, m, l)
+        elif gather is not None:
+            ringmod.gathered_context_attention(q, kv_local, o, m, l, rank=rank, lens=[T], P=P, metas=metas, plans=plans,
+                                               max_len_in_batch=Tl, num_kv_heads=H, attention_fn=ca.context_attention_fwd,
+                                               init_fn=init_fn, gather=gather)
         else:
             ringmod.ring_context_attention(q, kv_local, o, m, l, rank=rank, peers=list(range(P)), metas=metas,
                                            stride=stride, max_len_in_batch=Tl, num_kv_heads=H, comm=comm,
@@ -898,7 +909,7 @@ def main():
         torch.cuda.empty_cache()
         pipe = HostPrefillPipeline(Tl, max_tok, H, H, D, rank=rank, peers=list(range(P)), metas=metas, stride=stride,
                                    max_len_in_batch=Tl, comm=comm, head_chunks=chunks, device=dev, overlap=not args.no_overlap,
-                                   exchange=exchange)
+                                   exchange=exchange, gather=gather, lens=[T])
 
         def e2e_step():
             pipe.run(hq, hkv, ho)
@@ -932,9 +943,9 @@ def main():
         del hq, hkv, ho, pipe
         torch.cuda.empty_cache()
     st_flags2 = fd.device_status(clear=True)
-    if exchange is not None:
+    if exchange is not None or gather is not None:
         dist.barrier()
-        exchange.close()
+        (exchange if exchange is not None else gather).close()
 
     decode_nccl = decode_peer = None
     if not args.skip_extras and P > 1:
@@ -962,8 +973,11 @@ def main():
     parity["tolerance"] = "o: 2e-2 abs + 1e-2 rel; lse: 1e-3 abs + 1e-3 rel; against fp32 attention over the K/V rows of all ranks"
 
     if rank == 0:
-        exch = "single GPU" if P == 1 else ("copy-engine transfers into peer memory, flag-synchronised" if exchange is not None else
-                                            f"{'overlapped' if not args.no_overlap else 'serialised'} NCCL send/recv")
+        exch = ("single GPU" if P == 1 else
+                "every block copied into every instance's memory by copy engines while the local block is attended to, then one "
+                "launch over all gathered rows; flag-synchronised" if gather is not None else
+                "block-by-block ring, copy-engine transfers into peer memory, flag-synchronised" if exchange is not None else
+                f"block-by-block ring, {'overlapped' if not args.no_overlap else 'serialised'} NCCL send/recv")
         out = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": P, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
@@ -982,7 +996,9 @@ def main():
                          "peak_kind": "sustained cuBLAS bf16 (kernel runs for seconds inside the timed loop)",
                          "frac_of_burst_peak": per_gpu / peaks["tf_burst"], "per_gpu": True},
             "clocks": clocks,
-            "gpu_launches": args.steps * (1 + P) + (args.steps * 4 * (P - 1) if exchange is not None else 0),
+            # per pass: state reset + attention launches, plus the one-thread flag kernels of the copy-engine exchanges
+            "gpu_launches": args.steps * ((3 + 4 * (P - 1)) if gather is not None else
+                                          (1 + P) + (4 * (P - 1) if exchange is not None else 0)),
             "device_status": list(st), "flag_wait_status": [list(st_flags), list(st_flags2)],
             "parity_check": parity,
         }

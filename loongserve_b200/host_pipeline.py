@@ -28,16 +28,24 @@ class HostPrefillPipeline:
     """One instance's side of a ring prefill whose inputs and output are pinned host tensors.
 
     ``metas`` / ``stride`` / ``peers`` / ``comm`` / ``exchange`` as for ``ring.ring_context_attention`` (``comm`` may be None
-    for a ring of one or when ``exchange`` carries the blocks).  ``head_chunks`` must divide the number of KV heads.  Device scratch: two chunk-sized sets of q / kv / o / m / l
-    and, for a ring of more than one instance, two chunk-sized receive buffers."""
+    for a ring of one or when ``exchange`` carries the blocks).  With ``gather`` (a ``peer_ring.CopyEngineGather``) and
+    ``lens`` (the requests' global lengths) every chunk runs as ``ring.gathered_context_attention`` instead: two launches per
+    chunk, striped placement only.  ``head_chunks`` must divide the number of KV heads.  Device scratch: two chunk-sized
+    sets of q / kv / o / m / l and, for an NCCL ring of more than one instance, two chunk-sized receive buffers."""
 
     def __init__(self, q_tokens: int, max_token_num: int, num_q_heads: int, num_kv_heads: int, head_dim: int, *, rank: int,
                  peers: Sequence[int], metas: Sequence["ringmod.BlockMeta"], stride: int, max_len_in_batch: int, comm=None,
-                 head_chunks: int = 8, dtype=torch.bfloat16, device="cuda", overlap: bool = True, exchange=None):
+                 head_chunks: int = 8, dtype=torch.bfloat16, device="cuda", overlap: bool = True, exchange=None,
+                 gather=None, lens: Optional[Sequence[int]] = None):
         assert num_q_heads % num_kv_heads == 0 and num_kv_heads % head_chunks == 0
         self.Tq, self.Tkv, self.Hq, self.Hkv, self.D = q_tokens, max_token_num, num_q_heads, num_kv_heads, head_dim
         self.rank, self.peers, self.metas, self.stride, self.comm = rank, list(peers), metas, stride, comm
         self.max_len, self.overlap, self.exchange = max_len_in_batch, overlap, exchange
+        self.gather, self.lens = gather, (list(lens) if lens is not None else None)
+        if gather is not None:
+            assert lens is not None and stride == len(self.peers) and self.peers == list(range(len(self.peers))), \
+                "the gathered form needs the requests' lengths and a striped ring in rank order"
+            self.plans = [ringmod.GatherPlan.build(self.lens, len(self.peers), r, device) for r in range(len(self.peers))]
         self.n = head_chunks
         self.kc = num_kv_heads // head_chunks                 # kv heads per chunk
         self.qc = self.kc * (num_q_heads // num_kv_heads)     # q heads per chunk
@@ -49,7 +57,8 @@ class HostPrefillPipeline:
         self.m = [torch.empty((q_tokens, self.qc), dtype=torch.float32, device=dev) for _ in range(2)]
         self.l = [torch.empty((q_tokens, self.qc), dtype=torch.float32, device=dev) for _ in range(2)]
         # with a copy-engine exchange the blocks arrive in the exchange's own buffers
-        self.recv = [torch.empty_like(self.kv[0]) for _ in range(2)] if (len(self.peers) > 1 and exchange is None) else []
+        self.recv = ([torch.empty_like(self.kv[0]) for _ in range(2)]
+                     if (len(self.peers) > 1 and exchange is None and gather is None) else [])
         self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         self._ev = lambda: torch.cuda.Event()
         self._out_done: List[Optional[torch.cuda.Event]] = [None, None]     # o[b] has been copied out
@@ -96,6 +105,11 @@ class HostPrefillPipeline:
                 self._init_state(o, m, l)
                 ca.context_attention_fwd(q, kv[:, :self.kc], kv[:, self.kc:], o, me.start_loc, me.seq_len, me.first_idx, me.start_loc,
                                          me.seq_len, me.first_idx, self.stride, self.max_len, m, l)
+            elif self.gather is not None:
+                ringmod.gathered_context_attention(q, kv, o, m, l, rank=self.rank, lens=self.lens, P=len(self.peers),
+                                                   metas=self.metas, plans=self.plans, max_len_in_batch=self.max_len,
+                                                   num_kv_heads=self.kc, attention_fn=ca.context_attention_fwd,
+                                                   init_fn=self._init_state, gather=self.gather)
             else:
                 ringmod.ring_context_attention(q, kv, o, m, l, rank=self.rank, peers=self.peers, metas=self.metas, stride=self.stride,
                                                max_len_in_batch=self.max_len, num_kv_heads=self.kc, comm=self.comm,

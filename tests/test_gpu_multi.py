@@ -618,6 +618,70 @@ def test_graphed_decode_matches_kernel_by_kernel_decode_two_gpus(tmp_path):
                 assert bool(((a - b).abs() <= 1e-3 + 1e-3 * a.abs()).all()), (a - b).abs().max()
 
 
+def _gather_worker(rank, world, port, out):
+    """The two-launch form of a striped pass: blocks copied to every other instance by copy engines, flags in peer memory."""
+    dist, comm = _setup(rank, world, port)
+    from loongserve_b200 import context_attention as ca
+    from loongserve_b200 import ring
+    from loongserve_b200.peer_ring import CopyEngineGather
+    dev = torch.device("cuda", rank)
+    lens = [3000, 77, 1025, 1]
+    T, Hq, Hkv, D = sum(lens), 8, 4, 128
+    local_len, first, stride = ring.shard_lengths(lens, world, True)
+    max_tok = max(sum(x) for x in local_len)
+    metas = [ring.BlockMeta.from_lengths(local_len[r], first[r], dev) for r in range(world)]
+    plans = [ring.GatherPlan.build(lens, world, r, dev) for r in range(world)]
+    gather = CopyEngineGather(rank, world, max(p.rows for p in plans) * 2 * Hkv * D * 2, _gather_over(dist, world), device=dev)
+    res = {}
+    for pass_no in range(2):                  # the second pass reuses the gather buffer: credits and counters at work
+        g = torch.Generator().manual_seed(pass_no)
+        q = torch.randn(T, Hq, D, generator=g).to(torch.bfloat16)
+        k = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+        v = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+        qs = O.shard_tokens(q, lens, world, True)[rank].to(dev)
+        kv = torch.full((max_tok, 2 * Hkv, D), float("nan"), dtype=torch.bfloat16)
+        kr = O.shard_tokens(k, lens, world, True)[rank]; vr = O.shard_tokens(v, lens, world, True)[rank]
+        kv[:kr.shape[0], :Hkv] = kr; kv[:vr.shape[0], Hkv:] = vr
+        kv = kv.to(dev)
+        o = torch.empty_like(qs); m = torch.empty(qs.shape[0], Hq, device=dev); l = torch.empty(qs.shape[0], Hq, device=dev)
+        ring.gathered_context_attention(qs, kv, o, m, l, rank=rank, lens=lens, P=world, metas=metas, plans=plans,
+                                        max_len_in_batch=max(local_len[rank]), num_kv_heads=Hkv,
+                                        attention_fn=ca.context_attention_fwd, init_fn=ca.init_attention_state, gather=gather)
+        kv.fill_(float("nan"))                # what the next layer would do to the local block right after the pass
+        torch.cuda.synchronize()
+        res[pass_no] = dict(o=o.cpu(), lse=ca.attention_lse(m, l).cpu())
+    gather.check()
+    res["status"] = ca.device_status()
+    assert gather.passes == 2
+    dist.barrier()
+    gather.close()
+    torch.save(res, os.path.join(out, f"g{rank}.pt"))
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+
+
+def test_gathered_pass_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = min(torch.cuda.device_count(), 4)
+    mp.spawn(_gather_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    lens = [3000, 77, 1025, 1]
+    T, Hq, Hkv, D = sum(lens), 8, 4, 128
+    parts = [torch.load(os.path.join(str(tmp_path), f"g{r}.pt")) for r in range(world)]
+    assert all(p["status"][0] == 0 for p in parts)
+    for pass_no in range(2):
+        g = torch.Generator().manual_seed(pass_no)
+        q = torch.randn(T, Hq, D, generator=g).to(torch.bfloat16)
+        k = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+        v = torch.randn(T, Hkv, D, generator=g).to(torch.bfloat16)
+        ro, rlse = O.full_causal_attention(q, k, v, lens)
+        o = O.unshard_tokens([p[pass_no]["o"] for p in parts], lens, world, True)
+        lse = O.unshard_tokens([p[pass_no]["lse"] for p in parts], lens, world, True)
+        assert bool(((o.float() - ro).abs() <= 2e-2 + 1e-2 * ro.abs()).all())
+        assert torch.allclose(lse, rlse, atol=1e-3, rtol=1e-3)
+
+
 def _host_pipeline_worker(rank, world, port, out, exchange_kind="nccl"):
     """Ring prefill from pinned host buffers, pipelined over chunks of heads, against the plain device-resident ring."""
     dist, comm = _setup(rank, world, port)
@@ -644,30 +708,48 @@ def _host_pipeline_worker(rank, world, port, out, exchange_kind="nccl"):
     if exchange_kind == "copy_engine":
         from loongserve_b200.peer_ring import CopyEngineRing
         exchange = CopyEngineRing(rank, world, hkv.numel() * 2, _gather_over(dist, world), device=dev)
+    gather = plans = None
+    if exchange_kind == "gather":
+        from loongserve_b200.peer_ring import CopyEngineGather
+        plans = [ring.GatherPlan.build(lens, world, r, dev) for r in range(world)]
+        gather = CopyEngineGather(rank, world, max(p.rows for p in plans) * Hkv * D * 2, _gather_over(dist, world), device=dev)
     pipe = HostPrefillPipeline(hq.shape[0], max_tok, Hq, Hkv, D, rank=rank, peers=list(range(world)), metas=metas, stride=stride,
-                               max_len_in_batch=max(local_len[rank]), comm=comm, head_chunks=2, device=dev, exchange=exchange)
+                               max_len_in_batch=max(local_len[rank]), comm=comm, head_chunks=2, device=dev, exchange=exchange,
+                               gather=gather, lens=lens)
     pipe.run(hq, hkv, ho).synchronize()
     ho.zero_()
     pipe.run(hq, hkv, ho).synchronize()
     dq, dkv = hq.to(dev), hkv.to(dev)
     o = torch.empty_like(dq); m = torch.empty(dq.shape[0], Hq, device=dev); l = torch.empty(dq.shape[0], Hq, device=dev)
-    ring.ring_context_attention(dq, dkv, o, m, l, rank=rank, peers=list(range(world)), metas=metas, stride=stride,
-                                max_len_in_batch=max(local_len[rank]), num_kv_heads=Hkv, comm=comm,
-                                recv_buffers=[torch.empty_like(dkv), torch.empty_like(dkv)], attention_fn=ca.context_attention_fwd,
-                                init_fn=lambda o_, m_, l_: ca.init_attention_state(None, m_, l_))
+    if gather is not None:
+        # the device-resident run of the same form (all heads at once: its own, larger gather buffer)
+        big = CopyEngineGather(rank, world, max(p.rows for p in plans) * 2 * Hkv * D * 2, _gather_over(dist, world), device=dev)
+        ring.gathered_context_attention(dq, dkv, o, m, l, rank=rank, lens=lens, P=world, metas=metas, plans=plans,
+                                        max_len_in_batch=max(local_len[rank]), num_kv_heads=Hkv,
+                                        attention_fn=ca.context_attention_fwd,
+                                        init_fn=lambda o_, m_, l_: ca.init_attention_state(None, m_, l_), gather=big)
+        torch.cuda.synchronize()
+        big.check()
+        dist.barrier()
+        big.close()
+    else:
+        ring.ring_context_attention(dq, dkv, o, m, l, rank=rank, peers=list(range(world)), metas=metas, stride=stride,
+                                    max_len_in_batch=max(local_len[rank]), num_kv_heads=Hkv, comm=comm,
+                                    recv_buffers=[torch.empty_like(dkv), torch.empty_like(dkv)], attention_fn=ca.context_attention_fwd,
+                                    init_fn=lambda o_, m_, l_: ca.init_attention_state(None, m_, l_))
     torch.cuda.synchronize()
     torch.save(dict(same=bool(torch.equal(ho.view(torch.int16), o.cpu().view(torch.int16))), o=ho.clone(), status=ca.device_status()),
                os.path.join(out, f"hp{rank}.pt"))
-    if exchange is not None:
-        exchange.check()
+    if exchange is not None or gather is not None:
+        (exchange if exchange is not None else gather).check()
         dist.barrier()
-        exchange.close()
+        (exchange if exchange is not None else gather).close()
     dist.barrier()
     comm.close()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange_kind", ["nccl", "copy_engine"])
+@pytest.mark.parametrize("exchange_kind", ["nccl", "copy_engine", "gather"])
 def test_host_pipeline_ring_two_gpus(tmp_path, exchange_kind):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
