@@ -765,7 +765,9 @@ def main():
     ap.add_argument("--e2e-tokens", type=int, default=524288)
     ap.add_argument("--e2e-decode-steps", type=int, default=128)
     ap.add_argument("--e2e-layers", type=int, default=32)
-    ap.add_argument("--e2e-head-chunks", type=int, default=8, help="head chunks of the pipelined host-buffer leg")
+    ap.add_argument("--e2e-head-chunks", type=int, default=0,
+                    help="head chunks of the pipelined host-buffer leg (default: 16 on one GPU, where only the first upload and the "
+                         "last download are exposed and smaller chunks expose less; 8 on several, where every chunk is a ring pass)")
     ap.add_argument("--e2e-graph", action="store_true",
                     help="end-to-end run: replay the decode step as one CUDA graph per instance (implies --e2e-exchange peer_memory)")
     ap.add_argument("--e2e-exchange", default="nccl", choices=["nccl", "peer_memory"],
@@ -901,15 +903,32 @@ def main():
 
         # the public host-buffer call: chunks of heads pipelined over the copy engines and the ring
         from loongserve_b200.host_pipeline import HostPrefillPipeline
-        chunks = args.e2e_head_chunks
+        chunks = args.e2e_head_chunks if args.e2e_head_chunks > 0 else (16 if P == 1 else 8)
+        if gather is not None:
+            # the host-buffer leg runs the block-by-block form (see below): one untimed device-resident pass of that form
+            # gives the rows its result must equal bit for bit (the gathered form merges the partial softmaxes in another order)
+            from loongserve_b200.peer_ring import CopyEngineRing
+            ring_full = CopyEngineRing(rank, P, kv_local.numel() * 2, _gather_fn(dist, world), device=dev)
+            ringmod.ring_context_attention(q, kv_local, o, m, l, rank=rank, peers=list(range(P)), metas=metas, stride=stride,
+                                           max_len_in_batch=Tl, num_kv_heads=H, comm=comm, recv_buffers=None,
+                                           attention_fn=ca.context_attention_fwd, init_fn=init_fn, exchange=ring_full)
+            torch.cuda.synchronize()
+            ring_full.check()
+            dist.barrier()
+            ring_full.close()
         o_sample = o[:512].clone()                   # rows of the device-resident run, to check the host-buffer result against
         del o, m, l
         recv.clear()
         del q, kv_local
         torch.cuda.empty_cache()
+        # the host-buffer leg works on chunks of heads, whose rows are too short for the gathered form's strided copies
+        # (2 KiB per row and chunk: 96 ms per step at 8 GPUs against 78 ms block by block): it keeps the block-by-block ring
+        e2e_exchange = exchange
+        if gather is not None:
+            e2e_exchange = CopyEngineRing(rank, P, max_tok * 2 * (H // chunks) * D * 2, _gather_fn(dist, world), device=dev)
         pipe = HostPrefillPipeline(Tl, max_tok, H, H, D, rank=rank, peers=list(range(P)), metas=metas, stride=stride,
                                    max_len_in_batch=Tl, comm=comm, head_chunks=chunks, device=dev, overlap=not args.no_overlap,
-                                   exchange=exchange, gather=gather, lens=[T])
+                                   exchange=e2e_exchange)
 
         def e2e_step():
             pipe.run(hq, hkv, ho)
@@ -941,6 +960,9 @@ def main():
                "matches_device_run": bool(torch.equal(ho[:512].view(torch.int16), o_sample.cpu().view(torch.int16))),
                "api": "loongserve_b200.host_pipeline.HostPrefillPipeline.run(pinned q, kv, o)"}
         del hq, hkv, ho, pipe
+        if gather is not None:
+            dist.barrier()
+            e2e_exchange.close()
         torch.cuda.empty_cache()
     st_flags2 = fd.device_status(clear=True)
     if exchange is not None or gather is not None:

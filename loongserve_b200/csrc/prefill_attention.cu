@@ -373,10 +373,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                 tc_fence_after();
                 uint32_t sr[4][32];
                 tmem_ld32(tS, sr[0]);
-                tmem_ld32(tS + 32, sr[1]);
                 tmem_wait_ld();
-                tmem_ld32(tS + 64, sr[2]);          // second half streams in while the first is reduced
-                tmem_ld32(tS + 96, sr[3]);
+                tmem_ld32(tS + 32, sr[1]);          // every later chunk streams in while the one before it is worked on
                 const int n0 = j * BN;
                 const int r0 = m0 + t * BM;
                 const bool masked = (n0 + BN - 1 > vis_a * r0 + vis_c) || (n0 + BN > kv_len);
@@ -394,9 +392,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                     const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
                     uint32_t pa[32], pb[32];
                     const float s0 = chunk_exp<T, 0>(sr[0], scale, neg_m, pa);
+                    tmem_wait_ld();
+                    tmem_ld32(tS + 64, sr[2]);
                     const float s1 = chunk_exp<T, 16>(sr[1], scale, neg_m, pa);
                     tmem_wait_ld();
+                    tmem_ld32(tS + 96, sr[3]);
                     const float s2 = chunk_exp<T, 0>(sr[2], scale, neg_m, pb);
+                    tmem_wait_ld();
                     const float s3 = chunk_exp<T, 16>(sr[3], scale, neg_m, pb);
                     lsum = (s0 + s1) + (s2 + s3);
                     // no exponential can exceed the row's sum of them: a sum within 2^threshold proves that the tile's maximum
@@ -415,6 +417,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_step_kernel(
                     }
                 }
                 if (!published) {
+                    if (masked || j == 0) {
+                        tmem_wait_ld();
+                        tmem_ld32(tS + 64, sr[2]);
+                        tmem_ld32(tS + 96, sr[3]);
+                    }
                     float mx = fmaxf(chunk_max(sr[0], 0, limit, masked), chunk_max(sr[1], 32, limit, masked));
                     tmem_wait_ld();
                     mx = fmax3(mx, chunk_max(sr[2], 64, limit, masked), chunk_max(sr[3], 96, limit, masked));
@@ -732,10 +739,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_pair_kernel(
                 tc_fence_after();
                 uint32_t sr[4][32];
                 tmem_ld32(tS, sr[0]);
-                tmem_ld32(tS + 32, sr[1]);
                 tmem_wait_ld();
-                tmem_ld32(tS + 64, sr[2]);          // second half streams in while the first is reduced
-                tmem_ld32(tS + 96, sr[3]);
+                tmem_ld32(tS + 32, sr[1]);          // every later chunk streams in while the one before it is worked on
                 const int n0 = j * BN;
                 const int r0 = m0 + t * BM;
                 const bool masked = (n0 + BN - 1 > vis_a * r0 + vis_c) || (n0 + BN > kv_len);
@@ -753,9 +758,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_pair_kernel(
                     const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
                     uint32_t pa[32], pb[32];
                     const float s0 = chunk_exp<T, 0>(sr[0], scale, neg_m, pa);
+                    tmem_wait_ld();
+                    tmem_ld32(tS + 64, sr[2]);
                     const float s1 = chunk_exp<T, 16>(sr[1], scale, neg_m, pa);
                     tmem_wait_ld();
+                    tmem_ld32(tS + 96, sr[3]);
                     const float s2 = chunk_exp<T, 0>(sr[2], scale, neg_m, pb);
+                    tmem_wait_ld();
                     const float s3 = chunk_exp<T, 16>(sr[3], scale, neg_m, pb);
                     lsum = (s0 + s1) + (s2 + s3);
                     // no exponential can exceed the row's sum of them: a sum within 2^threshold proves that the tile's maximum
@@ -774,6 +783,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) prefill_pair_kernel(
                     }
                 }
                 if (!published) {
+                    if (masked || j == 0) {
+                        tmem_wait_ld();
+                        tmem_ld32(tS + 64, sr[2]);
+                        tmem_ld32(tS + 96, sr[3]);
+                    }
                     float mx = fmaxf(chunk_max(sr[0], 0, limit, masked), chunk_max(sr[1], 32, limit, masked));
                     tmem_wait_ld();
                     mx = fmax3(mx, chunk_max(sr[2], 64, limit, masked), chunk_max(sr[3], 96, limit, masked));

@@ -214,6 +214,18 @@ def test_gathered_blocks_on_one_gpu_equal_full_attention(P, long):
     _check(o, ro, lse, rlse)
 
 
+
+def test_strided_entry_rejects_strides_it_cannot_serve():
+    """The q position stride must be a positive multiple of the key position stride."""
+    ca = _ca()
+    q = torch.zeros(8, 2, 128, dtype=torch.float16, device=DEV)
+    m = torch.zeros(8, 2, device=DEV)
+    z = _i32([0]); n = _i32([8])
+    for sq, sk in ((3, 2), (1, 2), (4, 0)):
+        with pytest.raises(RuntimeError, match="bad argument|invalid"):
+            ca.context_attention_fwd(q, q, q, q.clone(), z, n, z, z, n, z, sq, 8, m, m.clone(), kv_pos_stride=sk)
+
+
 def test_unsupported_head_dim_is_rejected():
     ca = _ca()
     q = torch.zeros(8, 2, 64, dtype=torch.float16, device=DEV)
