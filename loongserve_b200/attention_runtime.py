@@ -39,7 +39,7 @@ class ESPAttentionRuntime:
     def __init__(self, *, layers_num: int, q_head_num: int, kv_head_num: int, head_dim: int, max_total_token_num: int,
                  max_req_num: int, max_seq_length: int, sp_world_size: int = 1, total_rank: int = 0, sp_comm=None,
                  dtype=torch.bfloat16, device="cuda", decode_block_seq: Optional[int] = None,
-                 peer_memory_decode="auto", peer_memory_max_batch: Optional[int] = None):
+                 peer_memory_decode="auto", peer_memory_max_batch: Optional[int] = None, gathered_prefill: bool = False):
         self.layers_num = layers_num
         self.tp_q_head_num_ = q_head_num
         self.tp_k_head_num_ = kv_head_num
@@ -56,6 +56,12 @@ class ESPAttentionRuntime:
                                                   num_idle_slots=sp_world_size, device=device)
         self.req_manager = LongServeReqManager(max_req_num, max_seq_length, self.mem_manager)
         self._fused_groups = {}
+        # Striped prefill passes over all instances in two attention launches instead of sp_world_size (every block copied to
+        # every instance by copy engines, ``ring.gathered_context_attention``): opt-in, for batches without scale-down
+        # bookkeeping whose request lengths are known on the host.  The exchange buffer is made at the first such batch and
+        # grown when a later one needs more (collective: all instances see the same batches).
+        self.gathered_prefill = bool(gathered_prefill) and sp_world_size > 1
+        self._gather = None
         # decode layer calls between two reads of the device status words (0 = never read them here)
         self.status_check_interval = 32 * 64
         self._decode_calls = 0
@@ -104,6 +110,19 @@ class ESPAttentionRuntime:
         for g in self._fused_groups.values():
             g.close()
         self._fused_groups = {}
+        if self._gather is not None:
+            self._gather.close()
+            self._gather = None
+
+    def _gather_exchange(self, nbytes: int):
+        """The gather buffer of this instance, at least ``nbytes`` large (every instance computes the same size)."""
+        if self._gather is None or self._gather.gathered_bytes < nbytes:
+            from .peer_ring import CopyEngineGather
+            if self._gather is not None:
+                self._gather.close()
+            self._gather = CopyEngineGather(self.total_rank_, self.sp_world_size, nbytes, self._ring_all_gather_bytes,
+                                            device=self.device)
+        return self._gather
 
     def check_device_status(self):
         """Raise if a bounded in-kernel wait ran out, or a kernel met a slot id outside the pool, on this device since
@@ -160,6 +179,12 @@ class ESPAttentionRuntime:
             local_len, first, stride = ringmod.shard_lengths(request_lengths, P, striped)
             st.block_metas = [ringmod.BlockMeta.from_lengths(local_len[r], first[r], self.device) for r in range(P)]
             st.stride = stride
+            if (self.gathered_prefill and striped and not need_context_migration and P == self.sp_world_size
+                    and st.logical_sp_peer_ranks == list(range(P)) and logical_sp_rank == self.total_rank_):
+                st.request_lengths = [int(x) for x in request_lengths]
+                st.gather_plans = [ringmod.GatherPlan.build(st.request_lengths, P, r, self.device) for r in range(P)]
+                row_bytes = H2 * self.head_dim_ * torch.empty((), dtype=self.dtype).element_size()
+                self._gather_exchange(max(p.rows for p in st.gather_plans) * row_bytes)
         elif P == 1:
             st.block_metas = [ringmod.BlockMeta(b_start_loc, b_seq_len, first_token_global_idx)]
             st.stride = 1
@@ -243,6 +268,13 @@ class ESPAttentionRuntime:
             if not st.need_context_migration:
                 kv_ops.destindex_copy_kv(kv[:st.total_token_num], st.mem_index, self.mem_manager.kv_buffer[layer_idx])
         o = torch.empty_like(q) if out is None else out
+        if getattr(st, "gather_plans", None) is not None:
+            ringmod.gathered_context_attention(
+                q.view(-1, Hq, D), kv, o.view(-1, Hq, D), st.local_m[:q.shape[0]], st.local_l[:q.shape[0]],
+                rank=st.logical_sp_rank, lens=st.request_lengths, P=P, metas=st.block_metas, plans=st.gather_plans,
+                max_len_in_batch=st.max_len_in_batch, num_kv_heads=Hkv, attention_fn=ca.context_attention_fwd,
+                init_fn=ca.init_attention_state, gather=self._gather)
+            return o
         ringmod.ring_context_attention(
             q.view(-1, Hq, D), kv, o.view(-1, Hq, D), st.local_m[:q.shape[0]], st.local_l[:q.shape[0]],
             rank=st.logical_sp_rank, peers=st.logical_sp_peer_ranks, metas=st.block_metas, stride=st.stride,

@@ -279,6 +279,67 @@ def _runtime_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
+def _runtime_gathered_worker(rank, world, port, out):
+    """Prefill batches through the runtime with ``gathered_prefill=True``: two attention launches per layer instead of one per
+    instance.  The second batch is larger than the first (the exchange buffer is remade, collectively), the third smaller."""
+    dist, comm = _setup(rank, world, port)
+    from loongserve_b200.attention_runtime import ESPAttentionRuntime
+    dev = torch.device("cuda", rank)
+    L, Hq, Hkv, D = 2, 8, 4, 128
+    rt = ESPAttentionRuntime(layers_num=L, q_head_num=Hq, kv_head_num=Hkv, head_dim=D, max_total_token_num=8192, max_req_num=8,
+                             max_seq_length=4096, sp_world_size=world, total_rank=rank, sp_comm=comm, dtype=torch.bfloat16,
+                             device=dev, peer_memory_decode=False, gathered_prefill=True)
+    res = []
+    for bi, lens in enumerate(([300, 64], [1500, 3, 777], [129])):
+        g = torch.Generator().manual_seed(50 + bi)
+        B, T = len(lens), sum(lens)
+        q = [torch.randn(T, Hq, D, generator=g).to(torch.bfloat16) for _ in range(L)]
+        kv = [torch.randn(T, 2 * Hkv, D, generator=g).to(torch.bfloat16) for _ in range(L)]
+        local_len = [max(0, (n - rank + world - 1) // world) for n in lens]
+        b_len = torch.tensor(local_len, dtype=torch.int32, device=dev)
+        b_start = torch.cumsum(b_len, 0, dtype=torch.int32) - b_len
+        b_req = torch.arange(B, dtype=torch.int32, device=dev)
+        max_tok = max(sum(max(0, (n - r + world - 1) // world) for n in lens) for r in range(world))
+        st = rt.prepare_prefill(B, sum(local_len), max_tok, max(max(local_len), 1), b_req, b_start, b_len,
+                                torch.full((B,), rank, dtype=torch.int32, device=dev), list(range(world)), rank,
+                                request_lengths=lens, striped=True)
+        assert getattr(st, "gather_plans", None) is not None
+        outs = []
+        for layer in range(L):
+            mine = O.shard_tokens(kv[layer], lens, world, True)[rank]
+            rt.pre_cache_kv(st, layer)[:mine.shape[0]].copy_(mine.to(dev))
+            o = rt.context_attention(O.shard_tokens(q[layer], lens, world, True)[rank].to(dev), st, layer)
+            outs.append(o.cpu())
+        torch.cuda.synchronize()
+        rt.check_device_status()
+        res.append(outs)
+        rt.mem_manager.free_all()
+        rt.req_manager.free_all()
+    torch.save(res, os.path.join(out, f"rg{rank}.pt"))
+    dist.barrier()
+    rt.close()
+    comm.close()
+    dist.destroy_process_group()
+
+
+def test_runtime_gathered_prefill_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    mp.spawn(_runtime_gathered_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    parts = [torch.load(os.path.join(str(tmp_path), f"rg{r}.pt")) for r in range(world)]
+    L, Hq, Hkv, D = 2, 8, 4, 128
+    for bi, lens in enumerate(([300, 64], [1500, 3, 777], [129])):
+        g = torch.Generator().manual_seed(50 + bi)
+        T = sum(lens)
+        q = [torch.randn(T, Hq, D, generator=g).to(torch.bfloat16) for _ in range(L)]
+        kv = [torch.randn(T, 2 * Hkv, D, generator=g).to(torch.bfloat16) for _ in range(L)]
+        for layer in range(L):
+            ro, _ = O.full_causal_attention(q[layer], kv[layer][:, :Hkv], kv[layer][:, Hkv:], lens)
+            o = O.unshard_tokens([p[bi][layer] for p in parts], lens, world, True)
+            assert bool(((o.float() - ro).abs() <= 2e-2 + 1e-2 * ro.abs()).all()), (bi, layer)
+
+
 class LongServeState:
     def __init__(self, master_plan, peer_plan, logical_sp_peer_ranks=None):
         self.master_plan, self.peer_plan, self.logical_sp_peer_ranks = master_plan, peer_plan, logical_sp_peer_ranks
