@@ -43,7 +43,8 @@ def prefill_flops(T: int) -> float:
 
 
 # DRAM traffic per launch of the dominant kernels, from ncu captures (profiles/*.md):
-#  prefill_step_kernel at 262144 tokens on 1 GPU: dram read 20.39 GB + write 2.81 GB (single-pass capture, full size);
+#  prefill at 262144 tokens on 1 GPU: dram read 20.39 GB + write 2.81 GB (single-pass full-size capture of the single-CTA kernel;
+#  the CTA-pair kernel moves the same bytes in the 32768-token capture, 1.08 GB, and was not captured at full size);
 #  decode_stage1_kernel: traffic / algorithmic bytes = 3.9958 / 3.9873 in the batch-8 capture, scaled by the units processed.
 PREFILL_TRAFFIC_262144_1GPU = 23.2e9
 DECODE_TRAFFIC_PER_ALG_BYTE = 3.9958 / 3.9873
@@ -1014,6 +1015,8 @@ def main():
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tf_sustained"], "unit": "TFLOP/s",
                          "frac": per_gpu / peaks["tf_sustained"],
                          "traffic": PREFILL_TRAFFIC_262144_1GPU if (P == 1 and T == T_TOTAL) else None,
+                         "traffic_source": "full-size single-pass ncu capture of the single-CTA kernel (the CTA-pair kernel reads the "
+                                           "same DRAM bytes in the 32768-token capture); 0.8 % of HBM bandwidth either way",
                          "peak_source": peaks["src"],
                          "peak_kind": "sustained cuBLAS bf16 (kernel runs for seconds inside the timed loop)",
                          "frac_of_burst_peak": per_gpu / peaks["tf_burst"], "per_gpu": True},
