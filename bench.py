@@ -756,6 +756,8 @@ def main():
     ap.add_argument("--exchange", default="gather", choices=["gather", "copy_engine", "nccl"],
                     help="KV exchange at N > 1: every block copied to every instance by copy engines, two attention launches per "
                          "pass (striped layout only); block-by-block ring with copy-engine transfers; or with ncclSend/ncclRecv")
+    ap.add_argument("--gather-parts", type=int, default=1,
+                    help="gathered form: position ranges the gathered rows are delivered and attended to in (one launch each)")
     ap.add_argument("--no-overlap", action="store_true", help="NCCL exchange only: queue it behind the attention kernel")
     ap.add_argument("--skip-extras", action="store_true", help="skip e2e / decode / cpu baseline (profiling runs)")
     ap.add_argument("--decode-only", action="store_true", help="run only the decode part (profiling runs)")
@@ -835,8 +837,9 @@ def main():
         exchange = CopyEngineRing(rank, P, kv_local.numel() * 2, _gather_fn(dist, world), device=dev)
     if P > 1 and args.exchange == "gather":
         from loongserve_b200.peer_ring import CopyEngineGather
-        plans = [ringmod.GatherPlan.build([T], P, r, dev) for r in range(P)]
-        gather = CopyEngineGather(rank, P, max(p_.rows for p_ in plans) * 2 * H * D * 2, _gather_fn(dist, world), device=dev)
+        plans = [ringmod.GatherPlan.build([T], P, r, dev, parts=args.gather_parts) for r in range(P)]
+        gather = CopyEngineGather(rank, P, max(p_.rows for p_ in plans) * 2 * H * D * 2, _gather_fn(dist, world), device=dev,
+                                  parts=args.gather_parts)
     recv = [torch.empty_like(kv_local) for _ in range(2 if (P > 1 and exchange is None and gather is None) else 0)]
     o = torch.empty_like(q)
     m = torch.empty(Tl, H, device=dev); l = torch.empty(Tl, H, device=dev)
@@ -997,8 +1000,9 @@ def main():
 
     if rank == 0:
         exch = ("single GPU" if P == 1 else
-                "every block copied into every instance's memory by copy engines while the local block is attended to, then one "
-                "launch over all gathered rows; flag-synchronised" if gather is not None else
+                "every block copied into every instance's memory by copy engines while the local block is attended to, then "
+                f"{'one launch' if args.gather_parts == 1 else str(args.gather_parts) + ' launches (position ranges)'} over all "
+                "gathered rows; flag-synchronised" if gather is not None else
                 "block-by-block ring, copy-engine transfers into peer memory, flag-synchronised" if exchange is not None else
                 f"block-by-block ring, {'overlapped' if not args.no_overlap else 'serialised'} NCCL send/recv")
         out = {
@@ -1022,7 +1026,7 @@ def main():
                          "frac_of_burst_peak": per_gpu / peaks["tf_burst"], "per_gpu": True},
             "clocks": clocks,
             # per pass: state reset + attention launches, plus the one-thread flag kernels of the copy-engine exchanges
-            "gpu_launches": args.steps * ((3 + 4 * (P - 1)) if gather is not None else
+            "gpu_launches": args.steps * ((2 + args.gather_parts + (2 + 2 * args.gather_parts) * (P - 1)) if gather is not None else
                                           (1 + P) + (4 * (P - 1) if exchange is not None else 0)),
             "device_status": list(st), "flag_wait_status": [list(st_flags), list(st_flags2)],
             "parity_check": parity,

@@ -213,14 +213,14 @@ class CopyEngineGather:
     interleaved in position order -- token n of the i-th other instance lands in row n*(P-1)+i of its request -- so that the
     gathered buffer reads like one block whose keys advance by one position per row.
 
-    Flags as in ``CopyEngineRing``: ``arrived[s]`` in the receiver's region counts the passes whose block sender s has
-    delivered, ``credit[r]`` in the sender's region the passes for which receiver r's buffer is free again.  Every wait is
-    bounded; ``check()`` reports an expired one."""
+    Flags as in ``CopyEngineRing``: ``arrived[s]`` in the receiver's region counts the position ranges (``parts`` per pass)
+    sender s has delivered, ``credit[r]`` in the sender's region the passes for which receiver r's buffer is free again.
+    Every wait is bounded; ``check()`` reports an expired one."""
 
     def __init__(self, rank: int, world: int, gathered_bytes: int, all_gather_bytes: Optional[Callable[[bytes], List[bytes]]],
-                 device="cuda", backend=None, peer_bases: Optional[List[int]] = None, raw_buffer=None):
-        assert 0 <= rank < world <= 64
-        self.rank, self.world = rank, world
+                 device="cuda", backend=None, peer_bases: Optional[List[int]] = None, raw_buffer=None, parts: int = 1):
+        assert 0 <= rank < world <= 64 and parts >= 1
+        self.rank, self.world, self.parts = rank, world, parts
         self.gathered_bytes = (int(gathered_bytes) + 255) // 256 * 256
         self.off_flags = self.gathered_bytes
         self.total = self.off_flags + 256 * 2
@@ -284,24 +284,27 @@ class CopyEngineGather:
         for p in self.streams:
             be.signal(S, self._credit_flag(p, self.rank), self.passes)
 
-    def push(self, peer: int, copies):
-        """Deliver this instance's block to ``peer``: ``copies`` is a list of ``(dst_offset_bytes, dst_pitch, src_address,
-        src_pitch, width_bytes, rows)`` strided copies into the peer's gather buffer.  The local block must be complete on
-        the compute stream when this is called."""
+    def push(self, peer: int, copies_per_part):
+        """Deliver this instance's block to ``peer``: for every position range, in order, a list of ``(dst_offset_bytes,
+        dst_pitch, src_address, src_pitch, width_bytes, rows)`` strided copies into the peer's gather buffer, announced when
+        they are done.  The local block must be complete on the compute stream when this is called."""
+        assert len(copies_per_part) == self.parts
         be, Cs = self.backend, self.streams[peer]
         be.wait(Cs, be.record(be.compute_stream()))
         be.flag_wait(Cs, self._credit_flag(self.rank, peer), self.passes, WAIT_GATHER_CREDIT)
-        for dst_off, dpitch, src, spitch, width, rows in copies:
-            assert dst_off + (rows - 1) * dpitch + width <= self.gathered_bytes if rows > 0 else True
-            be.copy2d(Cs, self.peer_base[peer] + dst_off, dpitch, src, spitch, width, rows)
-        be.signal(Cs, self._arrived_flag(peer, self.rank), self.passes)
+        for k, copies in enumerate(copies_per_part):
+            for dst_off, dpitch, src, spitch, width, rows in copies:
+                assert rows > 0 and dst_off + (rows - 1) * dpitch + width <= self.gathered_bytes
+                be.copy2d(Cs, self.peer_base[peer] + dst_off, dpitch, src, spitch, width, rows)
+            be.signal(Cs, self._arrived_flag(peer, self.rank), (self.passes - 1) * self.parts + k + 1)
         self._events.append(be.record(Cs))
 
-    def wait_all(self):
-        """The compute stream waits until every other instance's block of this pass has arrived."""
+    def wait_part(self, k: int):
+        """The compute stream waits until position range k of this pass has arrived from every other instance."""
+        assert 0 <= k < self.parts
         be, S = self.backend, self.backend.compute_stream()
         for p in self.streams:
-            be.flag_wait(S, self._arrived_flag(self.rank, p), self.passes, WAIT_GATHER_ARRIVAL)
+            be.flag_wait(S, self._arrived_flag(self.rank, p), (self.passes - 1) * self.parts + k + 1, WAIT_GATHER_ARRIVAL)
 
     def end_pass(self):
         """Later work on the compute stream sees this instance's own copies finished (the local block may be overwritten)."""

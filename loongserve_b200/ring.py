@@ -148,21 +148,41 @@ class GatherPlan:
     """Layout of one instance's gather buffer for a striped pass over ``P`` instances (``peer_ring.CopyEngineGather``):
     request b owns ``seq_len[b]`` rows from ``start_loc[b]``, holding the other instances' tokens of that request in
     position order (token n of the i-th other instance in row n*(P-1)+i).  Seen from there the local q row r of instance
-    ``rank`` sits at position r*(P-1) + rank - 1 (``q_first``), keys at 0, 1, 2, ..."""
+    ``rank`` sits at position r*(P-1) + rank - 1 (``q_first``), keys at 0, 1, 2, ...
+
+    With ``parts`` > 1 the rows of every request are cut into that many position ranges at multiples of P-1 rows (whole
+    groups of positions), each delivered and announced on its own, so that the attention over an early range can run while
+    the later ranges are still on their way: ``part_metas[k]`` describes range k as a block of its own (its keys start at
+    position ``first_idx`` = the range's first row), ``part_groups[b]`` holds the group boundaries of request b."""
     meta: BlockMeta                   # start_loc / seq_len of the gathered rows, first_idx = 0
     q_first: torch.Tensor             # int32 [batch], rank - 1
     rows: int
     start_rows: List[int]             # start_loc on the host
+    part_metas: List[BlockMeta] = field(default_factory=list)
+    part_groups: List[List[int]] = field(default_factory=list)
+    part_rows: List[int] = field(default_factory=list)
 
     @staticmethod
-    def build(lens: Sequence[int], P: int, rank: int, device):
+    def build(lens: Sequence[int], P: int, rank: int, device, parts: int = 1):
         local_len, _, _ = shard_lengths(lens, P, True)
         others = [int(L) - local_len[rank][b] for b, L in enumerate(lens)]
         meta = BlockMeta.from_lengths(others, [0] * len(lens), device)
         starts, acc = [], 0
         for n in others:
             starts.append(acc); acc += n
-        return GatherPlan(meta, torch.full((len(lens),), rank - 1, dtype=torch.int32).to(device), acc, starts)
+        plan = GatherPlan(meta, torch.full((len(lens),), rank - 1, dtype=torch.int32).to(device), acc, starts)
+        w = max(P - 1, 1)
+        for n in others:
+            groups = (n + w - 1) // w
+            plan.part_groups.append([groups * k // parts for k in range(parts + 1)])
+        for k in range(parts):
+            lo = [min(w * plan.part_groups[b][k], n) for b, n in enumerate(others)]
+            hi = [min(w * plan.part_groups[b][k + 1], n) for b, n in enumerate(others)]
+            i32 = lambda x: torch.tensor(x, dtype=torch.int32).to(device)
+            plan.part_metas.append(BlockMeta(i32([starts[b] + lo[b] for b in range(len(lens))]),
+                                             i32([hi[b] - lo[b] for b in range(len(lens))]), i32(lo)))
+            plan.part_rows.append(sum(hi[b] - lo[b] for b in range(len(lens))))
+        return plan
 
 
 def gathered_context_attention(q, local_kv, o, m, l, *, rank: int, lens: Sequence[int], P: int, metas: Sequence[BlockMeta],
@@ -170,11 +190,12 @@ def gathered_context_attention(q, local_kv, o, m, l, *, rank: int, lens: Sequenc
                                attention_fn: Callable, init_fn: Callable, gather):
     """One layer's prefill pass on instance ``rank`` of a STRIPED ring of ``P`` in two launches instead of P: every
     instance sends its block to all others with copy-engine transfers while it attends to its own block, then attends to
-    everything it was sent in one call.  Same result as ``ring_context_attention`` up to the order in which the partial
-    softmaxes are merged (longserve_transformer_layer_infer.py:128-181 does it block by block).  ``plans[r]`` is instance
-    r's ``GatherPlan`` (a pure function of the request lengths, so every instance can compute where its rows go in every
-    other instance's buffer).  Costs (P-1)/P of the whole KV of the batch in memory per instance; for batches where that is
-    too much, or scale-down bookkeeping is wanted (``keep``), use the ring."""
+    everything it was sent in one call (one call per position range when the plans were built with ``parts`` > 1).  Same
+    result as ``ring_context_attention`` up to the order in which the partial softmaxes are merged
+    (longserve_transformer_layer_infer.py:128-181 does it block by block).  ``plans[r]`` is instance r's ``GatherPlan`` (a
+    pure function of the request lengths, so every instance can compute where its rows go in every other instance's
+    buffer).  Costs (P-1)/P of the whole KV of the batch in memory per instance; for batches where that is too much, or
+    scale-down bookkeeping is wanted (``keep``), use the ring."""
     Hkv = num_kv_heads
     init_fn(o, m, l)
     me = metas[rank]
@@ -187,23 +208,32 @@ def gathered_context_attention(q, local_kv, o, m, l, *, rank: int, lens: Sequenc
     my_starts, acc = [], 0
     for n in local_len[rank]:
         my_starts.append(acc); acc += n
+    parts = len(plans[rank].part_metas)
+    assert parts == gather.parts, "the plans and the exchange were made for different numbers of position ranges"
     gather.begin_pass()
     for step in range(1, P):
         peer = (rank + step) % P
         i = rank if rank < peer else rank - 1           # this instance's place among the peer's other instances
-        copies = [((plans[peer].start_rows[b] + i) * row_bytes, (P - 1) * row_bytes,
-                   local_kv.data_ptr() + my_starts[b] * row_bytes, row_bytes, row_bytes, n)
-                  for b, n in enumerate(local_len[rank]) if n > 0]
-        gather.push(peer, copies)
+        per_part = []
+        for k in range(parts):
+            copies = []
+            for b, n in enumerate(local_len[rank]):
+                n0, n1 = min(plans[peer].part_groups[b][k], n), min(plans[peer].part_groups[b][k + 1], n)
+                if n1 > n0:
+                    copies.append(((plans[peer].start_rows[b] + n0 * (P - 1) + i) * row_bytes, (P - 1) * row_bytes,
+                                   local_kv.data_ptr() + (my_starts[b] + n0) * row_bytes, row_bytes, row_bytes, n1 - n0))
+            per_part.append(copies)
+        gather.push(peer, per_part)
     attention_fn(q, local_kv[:, :Hkv, :], local_kv[:, Hkv:, :], o, me.start_loc, me.seq_len, me.first_idx,
                  me.start_loc, me.seq_len, me.first_idx, P, max_len_in_batch, m, l)
-    gather.wait_all()
     plan = plans[rank]
-    if plan.rows > 0:
-        g = gather.gathered(plan.rows, local_kv)
-        attention_fn(q, g[:, :Hkv, :], g[:, Hkv:, :], o, me.start_loc, me.seq_len, plan.q_first,
-                     plan.meta.start_loc, plan.meta.seq_len, plan.meta.first_idx, P - 1, max_len_in_batch, m, l,
-                     kv_pos_stride=1)
+    g = gather.gathered(plan.rows, local_kv) if plan.rows > 0 else None
+    for k in range(parts):
+        gather.wait_part(k)
+        if plan.part_rows[k] > 0:
+            pm = plan.part_metas[k]
+            attention_fn(q, g[:, :Hkv, :], g[:, Hkv:, :], o, me.start_loc, me.seq_len, plan.q_first,
+                         pm.start_loc, pm.seq_len, pm.first_idx, P - 1, max_len_in_batch, m, l, kv_pos_stride=1)
     gather.end_pass()
     return o
 

@@ -679,7 +679,7 @@ def test_graphed_decode_matches_kernel_by_kernel_decode_two_gpus(tmp_path):
                 assert bool(((a - b).abs() <= 1e-3 + 1e-3 * a.abs()).all()), (a - b).abs().max()
 
 
-def _gather_worker(rank, world, port, out):
+def _gather_worker(rank, world, port, out, parts=1):
     """The two-launch form of a striped pass: blocks copied to every other instance by copy engines, flags in peer memory."""
     dist, comm = _setup(rank, world, port)
     from loongserve_b200 import context_attention as ca
@@ -691,8 +691,9 @@ def _gather_worker(rank, world, port, out):
     local_len, first, stride = ring.shard_lengths(lens, world, True)
     max_tok = max(sum(x) for x in local_len)
     metas = [ring.BlockMeta.from_lengths(local_len[r], first[r], dev) for r in range(world)]
-    plans = [ring.GatherPlan.build(lens, world, r, dev) for r in range(world)]
-    gather = CopyEngineGather(rank, world, max(p.rows for p in plans) * 2 * Hkv * D * 2, _gather_over(dist, world), device=dev)
+    plans = [ring.GatherPlan.build(lens, world, r, dev, parts=parts) for r in range(world)]
+    gather = CopyEngineGather(rank, world, max(p.rows for p in plans) * 2 * Hkv * D * 2, _gather_over(dist, world), device=dev,
+                              parts=parts)
     res = {}
     for pass_no in range(2):                  # the second pass reuses the gather buffer: credits and counters at work
         g = torch.Generator().manual_seed(pass_no)
@@ -722,11 +723,12 @@ def _gather_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_gathered_pass_two_gpus(tmp_path):
+@pytest.mark.parametrize("parts", [1, 2])
+def test_gathered_pass_two_gpus(tmp_path, parts):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     world = min(torch.cuda.device_count(), 4)
-    mp.spawn(_gather_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_gather_worker, args=(world, _free_port(), str(tmp_path), parts), nprocs=world, join=True)
     lens = [3000, 77, 1025, 1]
     T, Hq, Hkv, D = sum(lens), 8, 4, 128
     parts = [torch.load(os.path.join(str(tmp_path), f"g{r}.pt")) for r in range(world)]

@@ -206,8 +206,15 @@ def test_gathered_blocks_on_one_gpu_equal_full_attention(P, long):
         mx = max(max(local_len[r]), 1)
         ca.context_attention_fwd(qs[r].to(DEV), blk[:, :Hkv], blk[:, Hkv:], o, q_start, q_len, _i32(first[r]),
                                  q_start, q_len, _i32(first[r]), stride, mx, m, l)
-        ca.context_attention_fwd(qs[r].to(DEV), gk[:, :Hkv], gk[:, Hkv:], o, q_start, q_len, plan.q_first,
-                                 plan.meta.start_loc, plan.meta.seq_len, plan.meta.first_idx, P - 1, mx, m, l, kv_pos_stride=1)
+        if r % 2 == 0:
+            ca.context_attention_fwd(qs[r].to(DEV), gk[:, :Hkv], gk[:, Hkv:], o, q_start, q_len, plan.q_first,
+                                     plan.meta.start_loc, plan.meta.seq_len, plan.meta.first_idx, P - 1, mx, m, l, kv_pos_stride=1)
+        else:
+            # the same rows as three position ranges, one call each (what a pass does when the ranges arrive one by one)
+            plan3 = R.GatherPlan.build(lens, P, r, DEV, parts=3)
+            for pm in plan3.part_metas:
+                ca.context_attention_fwd(qs[r].to(DEV), gk[:, :Hkv], gk[:, Hkv:], o, q_start, q_len, plan.q_first,
+                                         pm.start_loc, pm.seq_len, pm.first_idx, P - 1, mx, m, l, kv_pos_stride=1)
         outs.append(o.cpu()); lses.append(ca.attention_lse(m, l).cpu())
     _status_ok()
     o = O.unshard_tokens(outs, lens, P, True); lse = O.unshard_tokens(lses, lens, P, True)

@@ -164,7 +164,7 @@ def test_a_missing_credit_is_detected_as_a_stuck_queue():
 
 
 # ------------------------------------------------------------------------------------------------ gather exchange
-def _build_gather(world, lens, seed, passes=2, hook=None):
+def _build_gather(world, lens, seed, passes=2, hook=None, parts=1):
     """The same harness around ``ring.gathered_context_attention`` and ``CopyEngineGather``: every instance sends its block
     to all others (one copy queue per peer) and attends to the local block and to the gathered rows."""
     g = torch.Generator().manual_seed(seed)
@@ -172,7 +172,7 @@ def _build_gather(world, lens, seed, passes=2, hook=None):
     local_len, first, stride = ring.shard_lengths(lens, world, True)
     max_tok = max(sum(x) for x in local_len)
     row_bytes = 2 * Hh * D * 4
-    plans = [ring.GatherPlan.build(lens, world, r, "cpu") for r in range(world)]
+    plans = [ring.GatherPlan.build(lens, world, r, "cpu", parts=parts) for r in range(world)]
     gbytes = (max(p.rows for p in plans) * row_bytes + 255) // 256 * 256
     sim = Sim(world)
     regions = [torch.full((gbytes + 512,), 0, dtype=torch.uint8) for _ in range(world)]
@@ -181,7 +181,7 @@ def _build_gather(world, lens, seed, passes=2, hook=None):
         reg[gbytes:].zero_()
     bases = [r.data_ptr() for r in regions]
     gathers = [CopyEngineGather(rank, world, gbytes, None, device="cpu", backend=Backend(sim, rank), peer_bases=bases,
-                                raw_buffer=regions[rank][:gbytes]) for rank in range(world)]
+                                raw_buffer=regions[rank][:gbytes], parts=parts) for rank in range(world)]
     if hook is not None:
         hook(gathers)
     outs, keep_alive = [], [regions]
@@ -218,11 +218,11 @@ def _build_gather(world, lens, seed, passes=2, hook=None):
     return sim, gathers, outs, keep_alive
 
 
-@pytest.mark.parametrize("world", [2, 3, 4, 8])
-def test_gather_every_interleaving_gives_full_attention(world):
+@pytest.mark.parametrize("world,parts", [(2, 1), (3, 1), (4, 1), (8, 1), (2, 2), (3, 2), (4, 3), (8, 2)])
+def test_gather_every_interleaving_gives_full_attention(world, parts):
     lens = [37, 5, 64, 1]
     for trial in range(5):
-        sim, gathers, outs, keep = _build_gather(world, lens, seed=trial, passes=2)
+        sim, gathers, outs, keep = _build_gather(world, lens, seed=trial, passes=2, parts=parts)
         sim.run(random.Random(77 * world + trial))
         for d in outs:
             ro, rlse = O.full_causal_attention(d["q"], d["k"], d["v"], lens)
