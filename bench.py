@@ -756,8 +756,9 @@ def main():
     ap.add_argument("--exchange", default="gather", choices=["gather", "copy_engine", "nccl"],
                     help="KV exchange at N > 1: every block copied to every instance by copy engines, two attention launches per "
                          "pass (striped layout only); block-by-block ring with copy-engine transfers; or with ncclSend/ncclRecv")
-    ap.add_argument("--gather-parts", type=int, default=1,
-                    help="gathered form: position ranges the gathered rows are delivered and attended to in (one launch each)")
+    ap.add_argument("--gather-parts", type=int, default=0,
+                    help="gathered form: position ranges the gathered rows are delivered and attended to in, one launch each "
+                         "(default: 2 on 8 or more GPUs, where the transfers outlast the attention over the local block; else 1)")
     ap.add_argument("--no-overlap", action="store_true", help="NCCL exchange only: queue it behind the attention kernel")
     ap.add_argument("--skip-extras", action="store_true", help="skip e2e / decode / cpu baseline (profiling runs)")
     ap.add_argument("--decode-only", action="store_true", help="run only the decode part (profiling runs)")
@@ -830,6 +831,8 @@ def main():
     q = torch.randn(Tl, H, D, generator=g, device=dev, dtype=torch.bfloat16)
     kv_local = torch.randn(max_tok, 2 * H, D, generator=g, device=dev, dtype=torch.bfloat16)
     exchange = gather = plans = None
+    if args.gather_parts <= 0:
+        args.gather_parts = 2 if P >= 8 else 1
     if P > 1 and args.exchange == "gather" and not striped:
         args.exchange = "copy_engine"            # the gathered form relies on the striped placement
     if P > 1 and args.exchange == "copy_engine":
