@@ -331,3 +331,51 @@ def test_migration_chunker_order_and_bookkeeping():
     calls.clear()
     out = rt.migrate_chunked(True, [1], [5], [9], 0, max_mig_len=100)
     assert calls == [([1], [5], [9], 5, 5)] and out == [14]
+
+
+@pytest.mark.parametrize("P", [2, 3, 5, 8])
+@pytest.mark.parametrize("parts", [1, 2, 3])
+def test_gather_plan_layout_is_dense_ordered_and_partitioned(P, parts):
+    """The layout of the gather buffer (ring.GatherPlan) and the copies ``gathered_context_attention`` derives from it, on
+    integers: every row of every instance's buffer is written exactly once, row m of a request holds the m-th token of the
+    other instances in position order, the position ranges partition the rows at whole groups of P-1, and the rows local q
+    row r may see (m <= r*(P-1) + rank - 1) are exactly the other instances' tokens at positions up to its own."""
+    from loongserve_b200 import ring
+    rng = np.random.default_rng(100 * P + parts)
+    lens = [int(x) for x in rng.integers(1, 90, size=5)] + [1, P, P + 1]
+    local_len, first, stride = ring.shard_lengths(lens, P, True)
+    plans = [ring.GatherPlan.build(lens, P, r, "cpu", parts=parts) for r in range(P)]
+    for recv in range(P):
+        plan = plans[recv]
+        buf = np.full(plan.rows, -1, dtype=np.int64)           # global position of the token each row holds
+        req = np.full(plan.rows, -1, dtype=np.int64)
+        for send in range(P):
+            if send == recv:
+                continue
+            i = send if send < recv else send - 1
+            for b, n in enumerate(local_len[send]):
+                for k in range(parts):
+                    n0, n1 = min(plan.part_groups[b][k], n), min(plan.part_groups[b][k + 1], n)
+                    for t in range(n0, n1):
+                        row = plan.start_rows[b] + t * (P - 1) + i
+                        assert buf[row] == -1, "a row written twice"
+                        buf[row] = send + t * P
+                        req[row] = b
+                        # the copy lands inside the range it is announced with
+                        pm = plan.part_metas[k]
+                        assert int(pm.start_loc[b]) <= row < int(pm.start_loc[b]) + int(pm.seq_len[b])
+        assert (buf >= 0).all(), "a row never written"
+        for b, L in enumerate(lens):
+            s0, n = plan.start_rows[b], int(plan.meta.seq_len[b])
+            want = [p for p in range(L) if p % P != recv]
+            assert n == len(want) and list(buf[s0:s0 + n]) == want and (req[s0:s0 + n] == b).all()
+            # the ranges partition the request's rows, cut at whole groups
+            lo = [int(plan.part_metas[k].first_idx[b]) for k in range(parts)]
+            ln = [int(plan.part_metas[k].seq_len[b]) for k in range(parts)]
+            assert lo[0] == 0 and all(lo[k] + ln[k] == (lo[k + 1] if k + 1 < parts else n) for k in range(parts))
+            assert all(x % (P - 1) == 0 for x in lo)
+            # visibility: local q row r (global position recv + r*P) sees exactly the rows up to r*(P-1) + recv - 1
+            for r in range(local_len[recv][b]):
+                limit = r * (P - 1) + int(plan.q_first[b])
+                visible = [m for m in range(n) if m <= limit]
+                assert [want[m] for m in visible] == [p for p in want if p <= recv + r * P]
