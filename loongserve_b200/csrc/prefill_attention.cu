@@ -12,12 +12,21 @@
 // The two q tiles ping-pong: while the tensor core runs tile 0's PV and next S, tile 1's softmax runs.
 // Tensor-memory map (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P aliases S.
 //
-// What bounds it.  The serial instruction stream of the one issuing thread is the critical path: a tcgen05.mma costs
-// that thread about 50 cycles to issue against 64 cycles of tensor-pipe time, so every wait, commit or spill reload in
-// its loop shows up as idle tensor pipe.  Hence: one wait and one commit per kv tile for the K/V data (pairs), a
+// Two kernels share this design: prefill_step_kernel (one CTA as described) and prefill_pair_kernel (a cluster of two CTAs
+// owns 512 rows; one thread issues cta_group::2 MMAs with M = 256 for both SMs, each CTA loading half of every K and V
+// tile; used whenever a request has more than 256 local rows).
+//
+// Visibility.  Key n of a request is visible to q row r iff q_first + r * q_pos_stride >= kv_first + n * kv_pos_stride
+// (and n < kv_len).  Within a ring step both strides are the ring size (striped placement) or 1; with q_pos_stride = P - 1
+// and kv_pos_stride = 1 one call covers the rows of all other instances gathered in position order.
+//
+// What bounds it.  Per q tile the chain S -> softmax -> PV is serial; the softmax needs one MUFU exponential per score
+// (16 per clock and SM: 1024 cycles per tile, as many as the tile's two MMAs need on the tensor pipe), and the one thread
+// that issues the MMAs (about 50 cycles per tcgen05.mma against 64 cycles of pipe time) shares the issue slots of its SM
+// sub-partition with two softmax warps.  Hence: one wait and one commit per kv tile for the K/V data (pairs), a
 // register budget for the third warpgroup that keeps the issue loop out of local memory, no votes or warp barriers in
-// the loop, and a softmax that takes its exponentials against the running maximum without first waiting for the
-// tile's own maximum (so the two tiles' dependent chains stay shorter than the issuer's loop).
+// the loop, and a softmax stripped to scale, exponential, sum and pack per score: exponentials are taken against the
+// running maximum, and the row sum they produce anyway proves that no score outgrew the lazy-rescale threshold.
 //
 // Roofline: tensor-core bound; algorithmic FLOPs = 4 * D * (visible q,k pairs) per head.
 // Every mbarrier wait is bounded; on expiry the kernel records a status word and drains.
