@@ -379,3 +379,52 @@ def test_gather_plan_layout_is_dense_ordered_and_partitioned(P, parts):
                 limit = r * (P - 1) + int(plan.q_first[b])
                 visible = [m for m in range(n) if m <= limit]
                 assert [want[m] for m in visible] == [p for p in want if p <= recv + r * P]
+
+
+def test_prefill_tile_arithmetic_covers_exactly_the_visible_keys():
+    """The tile bookkeeping of the prefill kernels (csrc/prefill_attention.cu: vis_a, vis_c, n_tiles, masked, limit; for CTA
+    pairs the tile count of a slot is that of the later CTA's rows), restated on integers and compared with the visibility
+    rule itself, q_first + r*q_pos_stride >= kv_first + n*kv_pos_stride and n < kv_len, for ring steps (equal strides),
+    the gathered form (key stride 1) and firsts of either sign: no visible key may fall outside the processed tiles, a tile
+    taken without masking must be visible to all rows of the q tile, and the per-row limit must be the last visible key."""
+    BM = BN = 128
+    rng = np.random.default_rng(7)
+
+    def floor_div(a, b):
+        return a // b                                    # Python's // is the floor for either sign, like the kernel's formula
+
+    cases = []
+    for _ in range(300):
+        sk = int(rng.choice([1, 1, 2, 3, 4, 8]))
+        a = 1 if rng.random() < 0.5 else int(rng.integers(1, 8))
+        sq = sk * a
+        cases.append((sq, sk, int(rng.integers(-40, 2000)), int(rng.integers(-40, 2000)), int(rng.integers(1, 700)),
+                      int(rng.integers(0, 3000))))
+    cases += [(7, 1, -1, 0, 600, 2500), (7, 1, 6, 0, 513, 3591), (1, 1, 0, 0, 300, 300), (8, 8, 3, 5, 400, 400)]
+    for sq, sk, q_first, kv_first, q_len, kv_len in cases:
+        vis_a = sq // sk
+        vis_c = floor_div(q_first - kv_first, sk)
+        rows = np.arange(q_len)
+        last_visible = np.minimum(floor_div(q_first + rows * sq - kv_first, sk), kv_len - 1)     # -1 or less: nothing visible
+        assert (np.minimum(vis_a * rows + vis_c, kv_len - 1) == last_visible).all()
+        for pairs in (False, True):
+            block = 2 * BM * (2 if pairs else 1)
+            for m0 in range(0, q_len, block):
+                for t in range(2):
+                    tile_rows = [m0 + c * 2 * BM + t * BM for c in ((0, 1) if pairs else (0,))]
+                    cnt = 0
+                    for r0 in tile_rows:
+                        if r0 < q_len:
+                            last_row = min(r0 + BM - 1, q_len - 1)
+                            rng_keys = max(0, min(vis_a * last_row + vis_c + 1, kv_len))
+                            cnt = max(cnt, (rng_keys + BN - 1) // BN)
+                    for r0 in tile_rows:
+                        if r0 >= q_len:
+                            continue
+                        rr = np.arange(r0, min(r0 + BM, q_len))
+                        assert (last_visible[rr] < cnt * BN).all(), "a visible key outside the processed tiles"
+                        for j in range(cnt):
+                            n0 = j * BN
+                            masked = (n0 + BN - 1 > vis_a * r0 + vis_c) or (n0 + BN > kv_len)
+                            if not masked:
+                                assert (last_visible[rr] >= n0 + BN - 1).all(), "an unmasked tile with an invisible key"
